@@ -9,8 +9,11 @@ encodings.
 
 The order in which layers run is data as well: `schedule` is a list of
 `ScheduleEntry`. An entry names the layer to run; the same layer may be named
-more than once (each run then has a cache of its own), and an entry may read
-the cache that an earlier entry wrote instead of keeping one.
+more than once (each run then has a cache of its own), an entry may read
+the cache that an earlier entry wrote instead of keeping one, and an entry may
+ask for the embedding's output to be added to the stream once more before it
+runs (models that pass a range of layers several times feed the input back in
+at the start of every further pass).
 """
 from __future__ import annotations
 
@@ -45,6 +48,7 @@ class LayerSpec:
 class ScheduleEntry:
     layer: int                          # index into ModelSpec.layers
     cache_from: Optional[int] = None    # schedule index whose cache this run reads, or None: its own
+    add_embedding: bool = False         # the embedding's output is added to the stream right before this run
 
 
 @dataclass(frozen=True)

@@ -39,7 +39,7 @@ constexpr int A_BYTES = BM * BK * 2;                 // 16 KB
 constexpr int THREADS = 192;
 constexpr int STAGING_BYTES = 32 * 128;              // 32 rows x 128 bytes per epilogue warp and buffer
 
-enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_GATED = 4 };
+enum Epi : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SWIGLU = 2, EPI_QKV = 3, EPI_GATED = 4, EPI_GELU = 5 };
 
 // The two epilogues that read a gate tile and its up tile side by side: SwiGLU, and the clamped gate
 // g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha g) * (u + 1).
@@ -583,12 +583,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                     for (int j = 0; j < 8; j++)
                         *reinterpret_cast<uint4*>(my_row + ((j ^ (lane & 7)) * 16)) = make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-                } else if (EPI == EPI_BF16) {
+                } else if (EPI == EPI_BF16 || EPI == EPI_GELU) {
 #pragma unroll
                     for (int half = 0; half < 2; half++) {
                         uint32_t r[32];
                         tc_ld32(t_row + c0 + half * 32, r);
                         add_parts(r, c0 + half * 32);
+                        if (EPI == EPI_GELU) {
+                            // the product rounded to bf16 first, as when it is stored before the activation; exact (erf) GELU
+#pragma unroll
+                            for (int e = 0; e < 32; e++) {
+                                const float z = round_to<bf16>(__uint_as_float(r[e]));
+                                r[e] = __float_as_uint(0.5f * z * (1.0f + erff(z * 0.7071067811865476f)));
+                            }
+                        }
 #pragma unroll
                         for (int j = 0; j < 4; j++) {
                             const uint4 v = make_uint4(pack2(__uint_as_float(r[8 * j]), __uint_as_float(r[8 * j + 1])),
@@ -921,14 +929,15 @@ MYNAH_API int mynah_gemm_tcgen05(const void* A, const void* W, void* C, int M, i
 
 // Grouped product: W stacks `groups` matrices of group_rows rows each ([groups * group_rows, K]); the rows of A are sorted
 // by matrix and every matrix's rows padded to whole tiles of 128, and tile_group[m] (device, M / 128 entries) names the
-// matrix of row tile m. epilogue 1: C fp32 [M, N], N <= group_rows output columns of the tile's matrix; 4: the clamped
+// matrix of row tile m. epilogue 1: C fp32 [M, N], N <= group_rows output columns of the tile's matrix; 5: the same with
+// the exact GELU on the rounded product, C bf16 [M, N]; 4: the clamped
 // gate, a matrix being N gate rows then N up rows (group_rows = 2 N), C bf16 [M, N]. M must be a multiple of 128.
 MYNAH_API int mynah_gemm_tcgen05_grouped(const void* A, const void* W, void* C, int M, int N, int K, int ldc, int epilogue,
                                          int groups, int group_rows, const int* tile_group, float gate_limit,
                                          float gate_alpha, int sm_count, int* status, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     MYNAH_REQUIRE(mynah_gemm_tcgen05_supported(M, N, K) && M % BM == 0, "gemm_tcgen05_grouped: M=%d N=%d K=%d is not taken", M, N, K);
-    MYNAH_REQUIRE((epilogue == EPI_F32 || epilogue == EPI_GATED) && ldc >= N, "gemm_tcgen05_grouped: bad epilogue or output stride");
+    MYNAH_REQUIRE((epilogue == EPI_F32 || epilogue == EPI_GATED || epilogue == EPI_GELU) && ldc >= N, "gemm_tcgen05_grouped: bad epilogue or output stride");
     MYNAH_REQUIRE(groups > 0 && tile_group != nullptr && group_rows >= (epilogue == EPI_GATED ? 2 * N : N),
                   "gemm_tcgen05_grouped: the matrices do not hold the product's rows");
     const int csize = epilogue == EPI_F32 ? 4 : 2;
@@ -944,6 +953,8 @@ MYNAH_API int mynah_gemm_tcgen05_grouped(const void* A, const void* W, void* C, 
         return launch_gemm<256, EPI_F32, 1>(ma, mb, mc, M, N, K, 0, sm_count, status, stream, QkvEpilogue{}, tile_group, group_rows);
     }
     if (make_map(&mc, C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, ldc, 32, 64)) return -1;
+    if (epilogue == EPI_GELU)
+        return launch_gemm<256, EPI_GELU, 1>(ma, mb, mc, M, N, K, 0, sm_count, status, stream, QkvEpilogue{}, tile_group, group_rows);
     return launch_gemm<256, EPI_GATED, 1>(ma, mb, mc, M, N, K, N, sm_count, status, stream, QkvEpilogue{}, tile_group, group_rows,
                                           gate_limit, gate_alpha);
 }

@@ -12,6 +12,13 @@
 //
 // Prompt steps in bfloat16 take another route to the same result: see "prompts in bfloat16" below.
 //
+// A second way to pick and to compute (the learned-router form):
+//   moe_router    logits z = W_r h + b_r in fp32; a token's experts are the `top` largest (the lower index wins a
+//                 tie), their weights the softmax over the chosen logits alone. It writes the choices and the
+//                 weights; moe_route then sorts by the choices instead of reading a table.
+//   act: plain    y = gelu(W_up,e h) (the exact, erf form), one matrix an expert, no gate
+//   moe_combine   out[t] = sum over the token's pairs of weight_pair * row
+//
 // The grid of the two products covers the most tiles a step can have (pairs / rows-per-tile + experts); CTAs
 // beyond the step's tiles leave at once, so a captured step needs no count from the host.
 #include "layout.cuh"
@@ -26,8 +33,8 @@ constexpr int MOE_MAX_EXPERTS = 1024;
 // tiles: [0] number of tiles, then per tile (expert, first index into perm, rows)
 __global__ void __launch_bounds__(MOE_ROUTE_THREADS)
 moe_route_kernel(const int* __restrict__ tokens, const int* __restrict__ tok_seq, const int* __restrict__ table,
-                 int T, int V, int top, int E, int BM, int* __restrict__ pair_expert, int* __restrict__ perm,
-                 int* __restrict__ tiles, int max_tiles, int* __restrict__ status) {
+                 const int* __restrict__ choice, int T, int V, int top, int E, int BM, int* __restrict__ pair_expert,
+                 int* __restrict__ perm, int* __restrict__ tiles, int max_tiles, int* __restrict__ status) {
     __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS];
     griddep_wait();
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
@@ -37,8 +44,12 @@ moe_route_kernel(const int* __restrict__ tokens, const int* __restrict__ tok_seq
         const int t = p / top;
         int e = -1;
         if (tok_seq[t] >= 0) {
-            const int tok = tokens[t];
-            if (tok >= 0 && tok < V) e = table[(size_t)tok * top + p % top];
+            if (choice != nullptr) {
+                e = choice[p];                                    // a router picked it
+            } else {
+                const int tok = tokens[t];
+                if (tok >= 0 && tok < V) e = table[(size_t)tok * top + p % top];
+            }
             if (e < 0 || e >= E) {
                 atomicOr(status, MYNAH_ST_TOKEN_RANGE);
                 e = -1;
@@ -70,13 +81,17 @@ moe_route_kernel(const int* __restrict__ tokens, const int* __restrict__ tok_seq
     }
 }
 
+enum MoeAct : int { MOE_ACT_CLAMPED_GATE = 0, MOE_ACT_GELU = 1 };
+
 struct MoeArgs {
     int top, D, F;
     float limit, alpha;
 };
 
+__device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.0f + erff(z * 0.7071067811865476f)); }
+
 // grid (tiles, column tiles of F). h: [T][D] rows; w_gu: [E][2][F][D] (gate rows, then up rows); y: [P][F]
-template <typename TA, int BM>
+template <typename TA, int BM, int ACT>
 __global__ void __launch_bounds__(tilemm::THREADS)
 moe_gate_up_kernel(const TA* __restrict__ h, const TA* __restrict__ w_gu, TA* __restrict__ y,
                    const int* __restrict__ perm, const int* __restrict__ tiles, MoeArgs a) {
@@ -92,10 +107,11 @@ moe_gate_up_kernel(const TA* __restrict__ h, const TA* __restrict__ w_gu, TA* __
         pair_s[i] = p;
         s.rows[i] = p >= 0 ? h + (size_t)(p / a.top) * a.D : nullptr;
     }
-    const TA* wg = w_gu + ((size_t)e * 2 * a.F + c0) * a.D;
+    constexpr int NMAT = ACT == MOE_ACT_CLAMPED_GATE ? 2 : 1;     // matrices an expert: gate and up, or up alone
+    const TA* wg = w_gu + ((size_t)e * NMAT * a.F + c0) * a.D;
     float g[BM / 16][BN / 16], u[BM / 16][BN / 16];
     tilemm::run<TA, BM, BN>(s, wg, (size_t)a.D, a.F - c0, a.D, g);
-    tilemm::run<TA, BM, BN>(s, wg + (size_t)a.F * a.D, (size_t)a.D, a.F - c0, a.D, u);
+    if (ACT == MOE_ACT_CLAMPED_GATE) tilemm::run<TA, BM, BN>(s, wg + (size_t)a.F * a.D, (size_t)a.D, a.F - c0, a.D, u);
     const int ty = threadIdx.x / 16, tx = threadIdx.x % 16;
 #pragma unroll
     for (int i = 0; i < BM / 16; i++) {
@@ -106,6 +122,10 @@ moe_gate_up_kernel(const TA* __restrict__ h, const TA* __restrict__ w_gu, TA* __
             const int c = c0 + tx + 16 * j;
             if (c >= a.F) continue;
             // the products are rounded to the activation type first, as a product kernel would store them
+            if (ACT == MOE_ACT_GELU) {
+                y[(size_t)p * a.F + c] = from_f32<TA>(gelu_erf_f(round_to<TA>(g[i][j])));
+                continue;
+            }
             const float gv = fminf(round_to<TA>(g[i][j]), a.limit);
             const float uv = fminf(fmaxf(round_to<TA>(u[i][j]), -a.limit), a.limit);
             y[(size_t)p * a.F + c] = from_f32<TA>(gv * (1.0f / (1.0f + expf(-a.alpha * gv))) * (uv + 1.0f));
@@ -145,9 +165,11 @@ moe_down_kernel(const TA* __restrict__ y, const TA* __restrict__ w_down, float* 
     }
 }
 
+// row_of_pair null: pair p's row is p. pair_weight null: every pair counts `weight`.
 template <typename TA>
-__global__ void moe_combine_kernel(const float* __restrict__ o, const int* __restrict__ pair_expert, TA* __restrict__ out,
-                                   int top, int D, float weight) {
+__global__ void moe_combine_kernel(const float* __restrict__ o, const int* __restrict__ pair_expert,
+                                   const int* __restrict__ row_of_pair, const float* __restrict__ pair_weight,
+                                   TA* __restrict__ out, int top, int D, float weight) {
     griddep_launch_small();
     griddep_wait();
     const int t = blockIdx.x;
@@ -155,10 +177,66 @@ __global__ void moe_combine_kernel(const float* __restrict__ o, const int* __res
         float acc = 0.f;
         for (int k = 0; k < top; k++) {
             const int p = t * top + k;
-            if (pair_expert[p] >= 0) acc += o[(size_t)p * D + c];
+            if (pair_expert[p] < 0) continue;
+            const float v = o[(size_t)(row_of_pair != nullptr ? row_of_pair[p] : p) * D + c];
+            acc = pair_weight != nullptr ? fmaf(pair_weight[p], v, acc) : acc + v;
         }
-        out[(size_t)t * D + c] = from_f32<TA>(acc * weight);
+        out[(size_t)t * D + c] = from_f32<TA>(pair_weight != nullptr ? acc : acc * weight);
     }
+}
+
+// The learned router: one CTA a token; a warp an expert's logit at a time, then one thread picks.
+constexpr int ROUTER_THREADS = 128;
+template <typename TA>
+__global__ void __launch_bounds__(ROUTER_THREADS)
+moe_router_kernel(const TA* __restrict__ h, const TA* __restrict__ w, VecRef bias, const int* __restrict__ tok_seq,
+                  int* __restrict__ choice, float* __restrict__ pair_weight, int D, int E, int top) {
+    __shared__ float z[MOE_MAX_EXPERTS];
+    griddep_wait();
+    const int t = blockIdx.x;
+    if (tok_seq[t] < 0) {
+        for (int k = threadIdx.x; k < top; k += blockDim.x) {
+            choice[t * top + k] = -1;
+            pair_weight[t * top + k] = 0.f;
+        }
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const TA* x = h + (size_t)t * D;
+    for (int e = warp; e < E; e += ROUTER_THREADS / 32) {
+        const TA* wr = w + (size_t)e * D;
+        float acc = 0.f;
+        for (int d = lane; d < D; d += 32) acc = fmaf(to_f32(x[d]), to_f32(wr[d]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc + bias.at(e);
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    // the largest logit `top` times over; lanes scan strided slices, the lower index wins a tie
+    float zmax = 0.f, sum = 0.f;
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int at = E;
+        for (int e = lane; e < E; e += 32)
+            if (z[e] > best) { best = z[e]; at = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (k == 0) zmax = best;
+        const float w_k = expf(best - zmax);
+        sum += w_k;
+        if (lane == 0) {
+            choice[t * top + k] = at < E ? at : -1;
+            pair_weight[t * top + k] = w_k;
+            if (at < E) z[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    const float inv = 1.0f / sum;
+    for (int k = lane; k < top; k += 32) pair_weight[t * top + k] *= inv;
 }
 
 // ---- the bfloat16 products on tensor cores (the core is in tile_mma.cuh) ----
@@ -167,7 +245,7 @@ constexpr int MMA_WARPS = 8;
 
 // grid (tiles, ceil(F / (8 warps * 8 NT columns))). A warp takes 8 NT columns of the gate and the same of the up matrix.
 // Decode steps (16-row tiles, mostly one row) take narrow warps, so that many CTAs stream the weights.
-template <int MT, int NT>
+template <int MT, int NT, int ACT>
 __global__ void __launch_bounds__(MMA_WARPS * 32, 2)
 moe_gate_up_mma_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w_gu, bf16* __restrict__ y,
                        const int* __restrict__ perm, const int* __restrict__ tiles, MoeArgs a) {
@@ -179,15 +257,16 @@ moe_gate_up_mma_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w_gu
     for (int i = threadIdx.x; i < 16 * MT; i += blockDim.x) pair_s[i] = i < nr ? perm[r0 + i] : -1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int c0 = (blockIdx.y * MMA_WARPS + warp) * (8 * NT);
-    const bf16* wrow[2][NT];
+    constexpr int NMAT = ACT == MOE_ACT_CLAMPED_GATE ? 2 : 1;     // matrices an expert: gate and up, or up alone
+    const bf16* wrow[NMAT][NT];
 #pragma unroll
     for (int j = 0; j < NT; j++) {
         const int c = min(c0 + j * 8 + g, a.F - 1);               // columns beyond F read the last row and are not stored
-        wrow[0][j] = w_gu + ((size_t)e * 2 * a.F + c) * a.D;
-        wrow[1][j] = wrow[0][j] + (size_t)a.F * a.D;
+        wrow[0][j] = w_gu + ((size_t)e * NMAT * a.F + c) * a.D;
+        if (NMAT == 2) wrow[NMAT - 1][j] = wrow[0][j] + (size_t)a.F * a.D;
     }
-    float acc[2][MT][NT][4];
-    tilemma::mma_tile<MT, NT, 2>(xs, pair_s, h, (size_t)a.D, a.top, wrow, a.D, acc);
+    float acc[NMAT][MT][NT][4];
+    tilemma::mma_tile<MT, NT, NMAT>(xs, pair_s, h, (size_t)a.D, a.top, wrow, a.D, acc);
 #pragma unroll
     for (int m = 0; m < MT; m++)
 #pragma unroll
@@ -200,8 +279,12 @@ moe_gate_up_mma_kernel(const bf16* __restrict__ h, const bf16* __restrict__ w_gu
                 for (int q = 0; q < 2; q++) {
                     const int c = c0 + j * 8 + 2 * t + q;
                     if (c >= a.F) continue;
+                    if (ACT == MOE_ACT_GELU) {
+                        y[(size_t)p * a.F + c] = from_f32<bf16>(gelu_erf_f(round_to<bf16>(acc[0][m][j][2 * half + q])));
+                        continue;
+                    }
                     const float gv = fminf(round_to<bf16>(acc[0][m][j][2 * half + q]), a.limit);
-                    const float uv = fminf(fmaxf(round_to<bf16>(acc[1][m][j][2 * half + q]), -a.limit), a.limit);
+                    const float uv = fminf(fmaxf(round_to<bf16>(acc[NMAT - 1][m][j][2 * half + q]), -a.limit), a.limit);
                     y[(size_t)p * a.F + c] = from_f32<bf16>(gv * (1.0f / (1.0f + expf(-a.alpha * gv))) * (uv + 1.0f));
                 }
         }
@@ -241,11 +324,11 @@ moe_down_mma_kernel(const bf16* __restrict__ y, const bf16* __restrict__ w_down,
         }
 }
 
-template <int MT>
+template <int MT, int ACT>
 int launch_products_mma(const void* h, const void* w_gu, const void* w_down, void* y, float* o, const int* perm,
                         const int* tiles, int max_tiles, const MoeArgs& a, cudaStream_t stream) {
     constexpr int NT_GU = MT == 1 ? 1 : 2, NT_DOWN = MT == 1 ? 1 : 4;
-    mynah_launch(moe_gate_up_mma_kernel<MT, NT_GU>, dim3(max_tiles, ceil_div(a.F, MMA_WARPS * 8 * NT_GU)), dim3(MMA_WARPS * 32), 0, stream,
+    mynah_launch(moe_gate_up_mma_kernel<MT, NT_GU, ACT>, dim3(max_tiles, ceil_div(a.F, MMA_WARPS * 8 * NT_GU)), dim3(MMA_WARPS * 32), 0, stream,
                  (const bf16*)h, (const bf16*)w_gu, (bf16*)y, perm, tiles, a);
     if (mynah_check_launch("moe_gate_up") != 0) return -1;
     mynah_launch(moe_down_mma_kernel<MT, NT_DOWN>, dim3(max_tiles, ceil_div(a.D, MMA_WARPS * 8 * NT_DOWN)), dim3(MMA_WARPS * 32), 0, stream,
@@ -261,7 +344,7 @@ constexpr int GROUP_TILE = 128;
 
 __global__ void __launch_bounds__(MOE_ROUTE_THREADS)
 moe_route_padded_kernel(const int* __restrict__ tokens, const int* __restrict__ tok_seq, const int* __restrict__ table,
-                        int T, int V, int top, int E, int m_pad, int* __restrict__ pair_expert, int* __restrict__ row_of_pair,
+                        const int* __restrict__ choice, int T, int V, int top, int E, int m_pad, int* __restrict__ pair_expert, int* __restrict__ row_of_pair,
                         int* __restrict__ perm_pad, int* __restrict__ tile_group, int* __restrict__ status) {
     __shared__ int count[MOE_MAX_EXPERTS], start[MOE_MAX_EXPERTS];
     griddep_wait();
@@ -273,8 +356,12 @@ moe_route_padded_kernel(const int* __restrict__ tokens, const int* __restrict__ 
         const int t = p / top;
         int e = -1;
         if (tok_seq[t] >= 0) {
-            const int tok = tokens[t];
-            if (tok >= 0 && tok < V) e = table[(size_t)tok * top + p % top];
+            if (choice != nullptr) {
+                e = choice[p];                                    // a router picked it
+            } else {
+                const int tok = tokens[t];
+                if (tok >= 0 && tok < V) e = table[(size_t)tok * top + p % top];
+            }
             if (e < 0 || e >= E) {
                 atomicOr(status, MYNAH_ST_TOKEN_RANGE);
                 e = -1;
@@ -317,25 +404,10 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ h, const int* __restr
     for (int i = threadIdx.x; i < D / 8; i += blockDim.x) dst[i] = src != nullptr ? src[i] : make_uint4(0u, 0u, 0u, 0u);
 }
 
-__global__ void moe_combine_rows_kernel(const float* __restrict__ o, const int* __restrict__ pair_expert,
-                                        const int* __restrict__ row_of_pair, bf16* __restrict__ out, int top, int D, float weight) {
-    griddep_launch_small();
-    griddep_wait();
-    const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < D; c += blockDim.x) {
-        float acc = 0.f;
-        for (int k = 0; k < top; k++) {
-            const int p = t * top + k;
-            if (pair_expert[p] >= 0) acc += o[(size_t)row_of_pair[p] * D + c];
-        }
-        out[(size_t)t * D + c] = from_f32<bf16>(acc * weight);
-    }
-}
-
-template <typename TA, int BM>
+template <typename TA, int BM, int ACT>
 int launch_products(const void* h, const void* w_gu, const void* w_down, void* y, float* o, const int* perm,
                     const int* tiles, int max_tiles, const MoeArgs& a, cudaStream_t stream) {
-    mynah_launch(moe_gate_up_kernel<TA, BM>, dim3(max_tiles, ceil_div(a.F, 64)), dim3(tilemm::THREADS), 0, stream,
+    mynah_launch(moe_gate_up_kernel<TA, BM, ACT>, dim3(max_tiles, ceil_div(a.F, 64)), dim3(tilemm::THREADS), 0, stream,
                  (const TA*)h, (const TA*)w_gu, (TA*)y, perm, tiles, a);
     if (mynah_check_launch("moe_gate_up") != 0) return -1;
     mynah_launch(moe_down_kernel<TA, BM>, dim3(max_tiles, ceil_div(a.D, 64)), dim3(tilemm::THREADS), 0, stream,
@@ -378,7 +450,73 @@ MYNAH_API int mynah_moe_tile_rows(int T, int top) { return (long long)T * top <=
 // Most tiles a step of T tokens can have.
 MYNAH_API int mynah_moe_max_tiles(int T, int top, int E) { return ceil_div(T * top, mynah_moe_tile_rows(T, top)) + E; }
 
-// The whole feed-forward. h: [T][D]; table: int32 [V][top]; w_gu: [E][2][F][D]; w_down: [E][D][F]; out: [T][D] in the
+// Both forms of the feed-forward. choice null: the table picks and every pair counts `weight`; else choice [T*top]
+// (a router's picks) and pair_weight [T*top]. act: MOE_ACT_*; out_f32: the result leaves as fp32 rows.
+static int moe_run(const void* h, int dtype, const int* tokens, const int* tok_seq, const int* table, const int* choice,
+                   const float* pair_weight, const void* w_gu, const void* w_down, void* out, int out_f32, void* y, float* o,
+                   int* ints, void* a_sorted, int T, int V, int top, int E, int D, int F, int act, float limit, float alpha,
+                   float weight, int* status, cudaStream_t stream) {
+    const int P = T * top, BM = mynah_moe_tile_rows(T, top), max_tiles = mynah_moe_max_tiles(T, top, E);
+    int* pair_expert = ints;
+    int* perm = ints + P;
+    int* tiles = ints + 2 * P;
+    const int threads = D >= 1024 ? 256 : 128;
+    const int m_pad = mynah_moe_grouped_rows(T, top, E, D, F, dtype);
+    if (m_pad > 0 && a_sorted != nullptr &&
+        (((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)y | (uintptr_t)a_sorted | (uintptr_t)o) & 15) == 0) {
+        int* perm_pad = ints + 2 * P + 1 + 3 * max_tiles;
+        int* tile_group = perm_pad + m_pad;
+        mynah_launch(moe_route_padded_kernel, dim3(1), dim3(MOE_ROUTE_THREADS), 0, stream, tokens, tok_seq, table, choice, T, V, top, E, m_pad,
+                     pair_expert, perm, perm_pad, tile_group, status);
+        if (mynah_check_launch("moe_route") != 0) return -1;
+        mynah_launch(moe_gather_kernel, dim3(m_pad), dim3(128), 0, stream, (const bf16*)h, (const int*)perm_pad, (bf16*)a_sorted, top, D);
+        if (mynah_check_launch("moe_gather") != 0) return -1;
+        if (act == MOE_ACT_GELU) {
+            if (mynah_gemm_tcgen05_grouped(a_sorted, w_gu, y, m_pad, F, D, F, 5, E, F, tile_group, 0.f, 0.f, 0, status, stream) != 0) return -1;
+        } else {
+            if (mynah_gemm_tcgen05_grouped(a_sorted, w_gu, y, m_pad, F, D, F, 4, E, 2 * F, tile_group, limit, alpha, 0, status, stream) != 0) return -1;
+        }
+        if (mynah_gemm_tcgen05_grouped(y, w_down, o, m_pad, D, F, D, 1, E, D, tile_group, 0.f, 0.f, 0, status, stream) != 0) return -1;
+        if (out_f32)
+            mynah_launch(moe_combine_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)o, (const int*)pair_expert,
+                         (const int*)perm, pair_weight, (float*)out, top, D, weight);
+        else
+            mynah_launch(moe_combine_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const float*)o, (const int*)pair_expert,
+                         (const int*)perm, pair_weight, (bf16*)out, top, D, weight);
+        return mynah_check_launch("moe_combine");
+    }
+    mynah_launch(moe_route_kernel, dim3(1), dim3(MOE_ROUTE_THREADS), 0, stream, tokens, tok_seq, table, choice, T, V, top, E, BM,
+                 pair_expert, perm, tiles, max_tiles, status);
+    if (mynah_check_launch("moe_route") != 0) return -1;
+    const MoeArgs a{top, D, F, limit, alpha};
+    int rc;
+    // bfloat16 rows that can move 16 bytes at a time take the tensor-core kernels
+    const bool mma_ok = dtype == MYNAH_BF16 && D % 8 == 0 && F % 8 == 0 && !g_moe_plain &&
+                        (((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)y) & 15) == 0;
+#define MOE_GO(ACT_)                                                                                                   \
+    if (mma_ok)                                                                                                        \
+        rc = BM == 16 ? launch_products_mma<1, ACT_>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream)         \
+                      : launch_products_mma<4, ACT_>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream);        \
+    else if (dtype == MYNAH_F32)                                                                                       \
+        rc = BM == 16 ? launch_products<float, 16, ACT_>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream)     \
+                      : launch_products<float, 64, ACT_>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream);    \
+    else                                                                                                               \
+        rc = BM == 16 ? launch_products<bf16, 16, ACT_>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream)      \
+                      : launch_products<bf16, 64, ACT_>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream)
+    if (act == MOE_ACT_GELU) { MOE_GO(MOE_ACT_GELU); }
+    else { MOE_GO(MOE_ACT_CLAMPED_GATE); }
+#undef MOE_GO
+    if (rc != 0) return rc;
+    if (dtype == MYNAH_F32 || out_f32)
+        mynah_launch(moe_combine_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)o, (const int*)pair_expert,
+                     (const int*)nullptr, pair_weight, (float*)out, top, D, weight);
+    else
+        mynah_launch(moe_combine_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const float*)o, (const int*)pair_expert,
+                     (const int*)nullptr, pair_weight, (bf16*)out, top, D, weight);
+    return mynah_check_launch("moe_combine");
+}
+
+// The whole feed-forward with a table. h: [T][D]; table: int32 [V][top]; w_gu: [E][2][F][D]; w_down: [E][D][F]; out: [T][D] in the
 // activation type. Scratch, with R = max(T*top, mynah_moe_grouped_rows(...)): y [R][F] (activation type), o fp32 [R][D],
 // ints [2*T*top + 1 + 3*max_tiles + R + R/128], and, when the products run grouped, a [R][D] (activation type; else null).
 MYNAH_API int mynah_moe_table_ffn(const void* h, int dtype, const int* tokens, const int* tok_seq, const int* table,
@@ -389,48 +527,30 @@ MYNAH_API int mynah_moe_table_ffn(const void* h, int dtype, const int* tokens, c
     MYNAH_REQUIRE(T > 0 && V > 0 && top > 0 && E > 0 && D > 0 && F > 0, "moe_table_ffn: bad sizes");
     MYNAH_REQUIRE(E <= MOE_MAX_EXPERTS, "moe_table_ffn: %d experts exceed %d", E, MOE_MAX_EXPERTS);
     MYNAH_REQUIRE(dtype == MYNAH_F32 || dtype == MYNAH_BF16, "moe_table_ffn: unsupported dtype %d", dtype);
-    const int P = T * top, BM = mynah_moe_tile_rows(T, top), max_tiles = mynah_moe_max_tiles(T, top, E);
-    int* pair_expert = ints;
-    int* perm = ints + P;
-    int* tiles = ints + 2 * P;
-    const int m_pad = mynah_moe_grouped_rows(T, top, E, D, F, dtype);
-    if (m_pad > 0 && a_sorted != nullptr &&
-        (((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)y | (uintptr_t)a_sorted | (uintptr_t)o) & 15) == 0) {
-        int* perm_pad = ints + 2 * P + 1 + 3 * max_tiles;
-        int* tile_group = perm_pad + m_pad;
-        mynah_launch(moe_route_padded_kernel, dim3(1), dim3(MOE_ROUTE_THREADS), 0, stream, tokens, tok_seq, table, T, V, top, E, m_pad,
-                     pair_expert, perm, perm_pad, tile_group, status);
-        if (mynah_check_launch("moe_route") != 0) return -1;
-        mynah_launch(moe_gather_kernel, dim3(m_pad), dim3(128), 0, stream, (const bf16*)h, (const int*)perm_pad, (bf16*)a_sorted, top, D);
-        if (mynah_check_launch("moe_gather") != 0) return -1;
-        if (mynah_gemm_tcgen05_grouped(a_sorted, w_gu, y, m_pad, F, D, F, 4, E, 2 * F, tile_group, limit, alpha, 0, status, stream) != 0) return -1;
-        if (mynah_gemm_tcgen05_grouped(y, w_down, o, m_pad, D, F, D, 1, E, D, tile_group, 0.f, 0.f, 0, status, stream) != 0) return -1;
-        mynah_launch(moe_combine_rows_kernel, dim3(T), dim3(D >= 1024 ? 256 : 128), 0, stream, (const float*)o, (const int*)pair_expert,
-                     (const int*)perm, (bf16*)out, top, D, weight);
-        return mynah_check_launch("moe_combine");
-    }
-    mynah_launch(moe_route_kernel, dim3(1), dim3(MOE_ROUTE_THREADS), 0, stream, tokens, tok_seq, table, T, V, top, E, BM,
-                 pair_expert, perm, tiles, max_tiles, status);
-    if (mynah_check_launch("moe_route") != 0) return -1;
-    const MoeArgs a{top, D, F, limit, alpha};
-    int rc;
-    // bfloat16 rows that can move 16 bytes at a time take the tensor-core kernels
-    const bool mma_ok = dtype == MYNAH_BF16 && D % 8 == 0 && F % 8 == 0 && !g_moe_plain &&
-                        (((uintptr_t)h | (uintptr_t)w_gu | (uintptr_t)w_down | (uintptr_t)y) & 15) == 0;
-    if (mma_ok)
-        rc = BM == 16 ? launch_products_mma<1>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream)
-                      : launch_products_mma<4>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream);
-    else if (dtype == MYNAH_F32)
-        rc = BM == 16 ? launch_products<float, 16>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream)
-                      : launch_products<float, 64>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream);
-    else
-        rc = BM == 16 ? launch_products<bf16, 16>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream)
-                      : launch_products<bf16, 64>(h, w_gu, w_down, y, o, perm, tiles, max_tiles, a, stream);
-    if (rc != 0) return rc;
-    const int threads = D >= 1024 ? 256 : 128;
+    return moe_run(h, dtype, tokens, tok_seq, table, nullptr, nullptr, w_gu, w_down, out, 0, y, o, ints, a_sorted, T, V, top, E,
+                   D, F, MOE_ACT_CLAMPED_GATE, limit, alpha, weight, status, stream);
+}
+
+// The feed-forward with a learned router: logits W_r h + b_r in fp32, the `top` largest, softmax over the chosen; experts
+// y = gelu(W_up h) (erf form), out = W_down y. w_router [E][D] in dtype, b_router [E] in b_dtype; w_up [E][F][D];
+// w_down [E][D][F]; out fp32 [T][D]. Scratch as above plus choice int [T*top] and pair_weight fp32 [T*top].
+MYNAH_API int mynah_moe_router_ffn(const void* h, int dtype, const int* tok_seq, const void* w_router, const void* b_router,
+                                   int b_dtype, const void* w_up, const void* w_down, float* out, void* y, float* o, int* ints,
+                                   void* a_sorted, int* choice, float* pair_weight, int T, int top, int E, int D, int F,
+                                   int* status, cudaStream_t stream) {
+    if (T == 0) return 0;
+    MYNAH_REQUIRE(T > 0 && top > 0 && E > 0 && top <= E && D > 0 && F > 0, "moe_router_ffn: bad sizes");
+    MYNAH_REQUIRE(E <= MOE_MAX_EXPERTS, "moe_router_ffn: %d experts exceed %d", E, MOE_MAX_EXPERTS);
+    const VecRef bias{b_router, b_dtype};
     if (dtype == MYNAH_F32)
-        mynah_launch(moe_combine_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)o, (const int*)pair_expert, (float*)out, top, D, weight);
+        mynah_launch(moe_router_kernel<float>, dim3(T), dim3(ROUTER_THREADS), 0, stream, (const float*)h, (const float*)w_router, bias,
+                     tok_seq, choice, pair_weight, D, E, top);
+    else if (dtype == MYNAH_BF16)
+        mynah_launch(moe_router_kernel<bf16>, dim3(T), dim3(ROUTER_THREADS), 0, stream, (const bf16*)h, (const bf16*)w_router, bias,
+                     tok_seq, choice, pair_weight, D, E, top);
     else
-        mynah_launch(moe_combine_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const float*)o, (const int*)pair_expert, (bf16*)out, top, D, weight);
-    return mynah_check_launch("moe_combine");
+        return mynah_fail("moe_router_ffn: unsupported dtype %d", dtype);
+    if (mynah_check_launch("moe_router") != 0) return -1;
+    return moe_run(h, dtype, nullptr, tok_seq, nullptr, choice, pair_weight, w_up, w_down, out, 1, y, o, ints, a_sorted, T, 1, top,
+                   E, D, F, MOE_ACT_GELU, 0.f, 0.f, 1.0f, status, stream);
 }

@@ -248,6 +248,7 @@ class Engine:
         self._prefetching = False                  # set while a captured decode step's launches are made
         self._layer_weights = [[t for p in self.model.layers[e.layer].parts() for t in p.streamed_tensors()]
                                for e in self.model.schedule]
+        self._feeds_embedding = any(e.add_embedding for e in self.model.schedule)
         self.launches = 0                          # kernels of this package launched (see count_launches)
         self.vocab_size = spec.vocab_size
 
@@ -346,11 +347,14 @@ class Engine:
         stream = Residual(x)
         if taps is not None:
             taps["embed"] = x.clone()
+        x0 = x.clone() if self._feeds_embedding else None      # the stream itself is added to in place
         views = self.cache.views
         ahead = self._ahead if self._prefetching else None
         for i, e in enumerate(self.model.schedule):
             if ahead is not None and i + 1 < len(self.model.schedule):
                 ahead.issue(self._layer_weights[i + 1])
+            if e.add_embedding:
+                stream.add_f32(x0)
             self.model.layers[e.layer].forward(stream, ctx, views[i])
             if taps is not None:
                 taps[f"layer{i}"] = stream.flush().clone()
@@ -498,7 +502,10 @@ class Engine:
 
     def _forward_layers_only(self, ctx: StepContext) -> None:
         stream = Residual(self._embed(ctx))
+        x0 = stream.x.clone() if self._feeds_embedding else None
         for i, e in enumerate(self.model.schedule):
+            if e.add_embedding:
+                stream.add_f32(x0)
             self.model.layers[e.layer].forward(stream, ctx, self.cache.views[i])
 
     def _embed(self, ctx: StepContext) -> torch.Tensor:

@@ -717,46 +717,67 @@ def selective_scan(x: torch.Tensor, z: torch.Tensor, dt_raw: torch.Tensor, Bm: t
     return y
 
 
-def delta_prep(qk: torch.Tensor, a_raw: torch.Tensor, b_raw: torch.Tensor, A_log: torch.Tensor, dt_bias: torch.Tensor,
-               H: int, G: int, dim: int):
-    """Unit q and k per head, beta and the decay of the gated delta rule (csrc/delta_rule.cu); all fp32."""
-    for t, n in ((qk, "q|k"), (a_raw, "a"), (b_raw, "b")):
-        _rows(t, "delta_prep: " + n)
-    if a_raw.stride(0) != b_raw.stride(0) or a_raw.dtype != qk.dtype or b_raw.dtype != qk.dtype:
-        raise KernelError("delta_prep: a and b must be column slices of one tensor of the activations' type")
+def delta_prep(qk: torch.Tensor, a_raw: Optional[torch.Tensor], b_raw: torch.Tensor, A_log: torch.Tensor,
+               dt_bias: torch.Tensor, H: int, G: int, dim: int, a_channels: Optional[torch.Tensor] = None):
+    """Unit q and k per head, beta and the decay of the gated delta rule (csrc/delta_rule.cu); all fp32. The decay is
+    one a head from a_raw [T, H], or, with a_channels (fp32 rows of H * dim values; dt_bias likewise), one a head and
+    key channel: g is then [T, H * dim]."""
+    _rows(qk, "delta_prep: q|k")
+    _rows(b_raw, "delta_prep: b")
+    if b_raw.dtype != qk.dtype:
+        raise KernelError("delta_prep: b must have the activations' type")
     T = qk.shape[0]
     dev = qk.device
+    if a_channels is None:
+        _rows(a_raw, "delta_prep: a")
+        if a_raw.stride(0) != b_raw.stride(0) or a_raw.dtype != qk.dtype:
+            raise KernelError("delta_prep: a and b must be column slices of one tensor of the activations' type")
+        g = torch.empty((T, H), dtype=torch.float32, device=dev)
+    else:
+        _rows(a_channels, "delta_prep: a per channel")
+        if a_channels.dtype != torch.float32 or a_channels.shape[1] != H * dim or dt_bias.numel() != H * dim:
+            raise KernelError("delta_prep: decays per channel need fp32 rows and a bias of heads x dim values")
+        g = torch.empty((T, H * dim), dtype=torch.float32, device=dev)
     qn = torch.empty((T, G * dim), dtype=torch.float32, device=dev)
     kn = torch.empty((T, G * dim), dtype=torch.float32, device=dev)
-    g = torch.empty((T, H), dtype=torch.float32, device=dev)
     beta = torch.empty((T, H), dtype=torch.float32, device=dev)
-    call("mynah_delta_prep", ptr(qk), qk.stride(0), ptr(a_raw), ptr(b_raw), a_raw.stride(0), code(qk.dtype),
-         ptr(A_log), ptr(dt_bias), code(A_log.dtype), ptr(qn), ptr(kn), ptr(g), ptr(beta), T, H, G, dim, stream_ptr())
+    call("mynah_delta_prep", ptr(qk), qk.stride(0), ptr(a_raw), ptr(b_raw), b_raw.stride(0), code(qk.dtype),
+         ptr(A_log), ptr(dt_bias), code(A_log.dtype), ptr(qn), ptr(kn), ptr(g), ptr(beta), T, H, G, dim,
+         ptr(a_channels), a_channels.stride(0) if a_channels is not None else 0, stream_ptr())
     return qn, kn, g, beta
 
 
 def delta_rule(qn: torch.Tensor, kn: torch.Tensor, v: torch.Tensor, g: torch.Tensor, beta: torch.Tensor,
-               state: torch.Tensor, ctx, H: int, G: int, dim: int, vd: int) -> torch.Tensor:
-    """The recurrence; state fp32 [max_seqs + 1, H, dim, vd]; returns o fp32 [T, H * vd]."""
+               state: torch.Tensor, ctx, H: int, G: int, dim: int, vd: int, channel_decay: bool = False) -> torch.Tensor:
+    """The recurrence; state fp32 [max_seqs + 1, H, dim, vd]; returns o fp32 [T, H * vd]. g fp32 [T, H], or
+    [T, H * dim] with channel_decay (one decay a head and key channel)."""
     _rows(v, "delta_rule: v")
     _chk(state, "delta state", torch.float32, 4)
     if tuple(state.shape[1:]) != (H, dim, vd):
         raise KernelError("delta_rule: the state does not fit")
     T = v.shape[0]
+    _chk(g, "decay", torch.float32, 2)
+    if g.shape[1] != (H * dim if channel_decay else H):
+        raise KernelError("delta_rule: the decay's rows do not fit")
+    channel = 1 if channel_decay else 0
     o = torch.empty((T, H * vd), dtype=torch.float32, device=v.device)
     call("mynah_delta_rule", ptr(qn), ptr(kn), ptr(v), v.stride(0), code(v.dtype), ptr(g), ptr(beta), ptr(state),
-         state.shape[0] - 1, ptr(o), ptr(ctx.cu_q), ptr(ctx.slots), ctx.B, H, G, dim, vd, stream_ptr())
+         state.shape[0] - 1, ptr(o), ptr(ctx.cu_q), ptr(ctx.slots), ctx.B, H, G, dim, vd, channel, stream_ptr())
     return o
 
 
-def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, H: int, vd: int, eps: float) -> torch.Tensor:
-    """o / rms(o per head) * w * silu(gate); o fp32 [T, H * vd], gate rows in the activation type."""
+def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, H: int, vd: int, eps: float,
+                  gate_act: str = "silu") -> torch.Tensor:
+    """o / rms(o per head) * w * act(gate), act silu or sigmoid; o fp32 [T, H * vd], gate rows (any of the two types),
+    the output in the gate's type."""
     _chk(o, "o", torch.float32, 2)
     _rows(gate, "gated_rmsnorm: gate")
+    if gate_act not in ("silu", "sigmoid"):
+        raise KernelError(f"gated_rmsnorm: gate activation {gate_act!r} is neither 'silu' nor 'sigmoid'")
     T = o.shape[0]
     out = torch.empty((T, H * vd), dtype=gate.dtype, device=o.device)
     call("mynah_gated_rmsnorm", ptr(o), ptr(gate), gate.stride(0), code(gate.dtype), ptr(w), code(w.dtype), ptr(out),
-         T, H, vd, float(eps), stream_ptr())
+         T, H, vd, float(eps), 1 if gate_act == "sigmoid" else 0, stream_ptr())
     return out
 
 
@@ -956,3 +977,167 @@ def moe_table_ffn(h: torch.Tensor, table: torch.Tensor, w_gu: torch.Tensor, w_do
          1.0 / top, ptr(ctx.status), stream_ptr())
     lib.add_launches(4 if grouped else 3)     # route, (gather,) two products, combine
     return out
+
+
+def moe_router_ffn(h: torch.Tensor, w_router: torch.Tensor, b_router: torch.Tensor, w_up: torch.Tensor,
+                   w_down: torch.Tensor, ctx, top: int) -> torch.Tensor:
+    """Experts picked by a learned router (fp32 logits W_r h + b_r, the `top` largest, softmax over the chosen alone);
+    an expert is W_down gelu_erf(W_up h) (csrc/moe.cu). w_router [E, D], b_router [E], w_up [E, F, D], w_down
+    [E, D, F]; returns fp32 [T, D]: the weighted sum is not rounded to the rows' type."""
+    _chk(h, "rows", dim=2)
+    _chk(w_router, "router weights", h.dtype, 2)
+    _chk(b_router, "router bias", dim=1)
+    _chk(w_up, "up weights", h.dtype, 3)
+    _chk(w_down, "down weights", h.dtype, 3)
+    T, D = h.shape
+    E, F, _ = w_up.shape
+    if (tuple(w_up.shape) != (E, F, D) or tuple(w_down.shape) != (E, D, F) or tuple(w_router.shape) != (E, D)
+            or b_router.numel() != E or not 1 <= top <= E):
+        raise KernelError("moe_router_ffn: sizes do not fit")
+    P_ = T * top
+    dev = h.device
+    grouped = int(lib.load().mynah_moe_grouped_rows(T, top, E, D, F, code(h.dtype)))
+    R = max(P_, grouped)
+    out = torch.empty((T, D), dtype=torch.float32, device=dev)
+    y = torch.empty((R, F), dtype=h.dtype, device=dev)
+    o = torch.empty((R, D), dtype=torch.float32, device=dev)
+    a = torch.empty((R, D), dtype=h.dtype, device=dev) if grouped else None
+    ints = torch.empty((3 * P_ + 1 + 3 * int(lib.load().mynah_moe_max_tiles(T, top, E)) + R + R // 128 + 1,),
+                       dtype=torch.int32, device=dev)
+    weights = torch.empty((P_,), dtype=torch.float32, device=dev)
+    choice = ints[ints.numel() - P_:]
+    call("mynah_moe_router_ffn", ptr(h), code(h.dtype), ptr(ctx.tok_seq), ptr(w_router), ptr(b_router), code(b_router.dtype),
+         ptr(w_up), ptr(w_down), ptr(out), ptr(y), ptr(o), ptr(ints), ptr(a), ptr(choice), ptr(weights), T, top, E, D, F,
+         ptr(ctx.status), stream_ptr())
+    lib.add_launches(5 if grouped else 4)     # router, route, (gather,) two products, combine
+    return out
+
+
+def rmsnorm_add(x: torch.Tensor, y: torch.Tensor, gain: torch.Tensor, eps: float, extra: Optional[torch.Tensor] = None,
+                gain2: Optional[torch.Tensor] = None, eps2: float = 0.0) -> Optional[torch.Tensor]:
+    """x <- x (+ extra) + y / rms(y) * gain, all fp32 (csrc/norm_post.cu); with gain2 also returns the RMS norm of the
+    new x under gain2 and eps2 as fp32 rows."""
+    _chk(x, "residual", torch.float32, 2)
+    _chk(y, "sublayer output", torch.float32, 2)
+    _chk(gain, "norm gain", dim=1)
+    T, D = x.shape
+    if y.shape != x.shape or gain.numel() != D or (extra is not None and (extra.shape != x.shape or extra.dtype != torch.float32)):
+        raise KernelError("rmsnorm_add: shapes differ")
+    h = None
+    if gain2 is not None:
+        _chk(gain2, "second norm gain", dim=1)
+        if gain2.numel() != D:
+            raise KernelError("rmsnorm_add: the second gain does not fit the rows")
+        h = torch.empty((T, D), dtype=torch.float32, device=x.device)
+    call("mynah_rmsnorm_add", ptr(x), ptr(y), ptr(extra), ptr(gain), code(gain.dtype), float(eps), ptr(gain2),
+         code(gain2.dtype) if gain2 is not None else 0, float(eps2), ptr(h), T, D, stream_ptr())
+    return h
+
+
+def rms_pair_mean(a: torch.Tensor, b: torch.Tensor, ga: torch.Tensor, gb: torch.Tensor, eps: float,
+                  weight: float) -> torch.Tensor:
+    """weight * (a / rms(a) * ga + b / rms(b) * gb), fp32 rows in and out (csrc/norm_post.cu)."""
+    _chk(a, "first branch", torch.float32, 2)
+    _chk(b, "second branch", torch.float32, 2)
+    _chk(ga, "first gain", dim=1)
+    _chk(gb, "second gain", ga.dtype, 1)
+    T, D = a.shape
+    if b.shape != a.shape or ga.numel() != D or gb.numel() != D:
+        raise KernelError("rms_pair_mean: shapes differ")
+    out = torch.empty((T, D), dtype=torch.float32, device=a.device)
+    call("mynah_rms_pair_mean", ptr(a), ptr(b), ptr(ga), ptr(gb), code(ga.dtype), float(eps), float(weight), ptr(out), T, D,
+         stream_ptr())
+    return out
+
+
+def rglru_in(p: torch.Tensor, y_off: int, x_off: int, width: int, by: torch.Tensor, bx: torch.Tensor):
+    """The recurrent unit's two branches from their stacked projection p [T, >= 2 * width]: y = gelu_tanh(p_y + b_y) in p's
+    type, x = p_x + b_x in fp32 (csrc/rglru.cu)."""
+    _rows(p, "rglru_in: projection")
+    _chk(by, "gate bias", dim=1)
+    _chk(bx, "input bias", by.dtype, 1)
+    T = p.shape[0]
+    if by.numel() != width or bx.numel() != width or max(y_off, x_off) + width > p.shape[1]:
+        raise KernelError("rglru_in: sizes do not fit")
+    y = torch.empty((T, width), dtype=p.dtype, device=p.device)
+    x = torch.empty((T, width), dtype=torch.float32, device=p.device)
+    call("mynah_rglru_in", ptr(p), p.stride(0), y_off, x_off, code(p.dtype), ptr(by), ptr(bx), code(by.dtype), ptr(y), ptr(x),
+         T, width, stream_ptr())
+    return y, x
+
+
+def rglru_gates(u: torch.Tensor, ra: torch.Tensor, ri: torch.Tensor, ba: torch.Tensor, bi: torch.Tensor, lam: torch.Tensor,
+                decay_scale: float):
+    """a = exp(-decay_scale * sigmoid(Ra u + ba) * softplus(lam)) and b = sqrt(1 - a^2) * sigmoid(Ri u + bi) * u with
+    block-diagonal Ra, Ri [blocks, bw, bw]; u fp32 [T, width]; both results fp32 (csrc/rglru.cu)."""
+    _chk(u, "recurrent input", torch.float32, 2)
+    _chk(ra, "recurrence gate weights", dim=3)
+    _chk(ri, "input gate weights", ra.dtype, 3)
+    T, width = u.shape
+    blocks, bw, _ = ra.shape
+    if tuple(ra.shape) != (blocks, bw, bw) or ri.shape != ra.shape or blocks * bw != width:
+        raise KernelError("rglru_gates: the gates' matrices do not fit the channels")
+    for t, n in ((ba, "recurrence gate bias"), (bi, "input gate bias"), (lam, "decay parameter")):
+        _chk(t, n, ba.dtype)
+        if t.numel() != width:
+            raise KernelError(f"rglru_gates: {n} does not fit the channels")
+    a = torch.empty((T, width), dtype=torch.float32, device=u.device)
+    b = torch.empty((T, width), dtype=torch.float32, device=u.device)
+    call("mynah_rglru_gates", ptr(u), ptr(ra), ptr(ri), code(ra.dtype), ptr(ba), ptr(bi), ptr(lam), code(ba.dtype),
+         float(decay_scale), ptr(a), ptr(b), T, width, blocks, stream_ptr())
+    return a, b
+
+
+def rglru_scan(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, state: torch.Tensor, ctx) -> torch.Tensor:
+    """S <- a S + b along each sequence of the step, S fp32 per slot ([max_seqs + 1, width]); returns S * y in y's type."""
+    _chk(a, "decay", torch.float32, 2)
+    _chk(b, "input", torch.float32, 2)
+    _chk(y, "gate branch", dim=2)
+    _chk(state, "recurrent state", torch.float32, 2)
+    T, width = a.shape
+    if b.shape != a.shape or y.shape != a.shape or state.shape[1] != width:
+        raise KernelError("rglru_scan: shapes differ")
+    out = torch.empty((T, width), dtype=y.dtype, device=y.device)
+    call("mynah_rglru_scan", ptr(a), ptr(b), ptr(y), code(y.dtype), ptr(state), state.shape[0] - 1, ptr(out), ptr(ctx.cu_q),
+         ptr(ctx.slots), ctx.B, width, stream_ptr())
+    return out
+
+
+def sink_attn_prep(qkv: torch.Tensor, q_out: torch.Tensor, k_cache, v_cache, cos_k, sin_k, cos_v: torch.Tensor,
+                   sin_v: torch.Tensor, ctx, pages: PageTableView, H: int, G: int, dim: int, vd: int, rot: int,
+                   interleaved: bool) -> None:
+    """Rotates q and k over their first `rot` dimensions and v over all of its own, writes k and v to the cache pages
+    and q to q_out (csrc/sink_attn.cu). k_cache None: only the queries."""
+    _rows(qkv, "sink_attn_prep: projection")
+    _chk(q_out, "q", qkv.dtype, 2)
+    if qkv.shape[1] < H * dim + (G * (dim + vd) if k_cache is not None else 0) or q_out.shape[1] != H * dim:
+        raise KernelError("sink_attn_prep: the projection's rows are too short")
+    if k_cache is not None:
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+            raise KernelError("sink_attn_prep: the cache and the activations differ in dtype")
+        if tuple(k_cache.shape[1:]) != (G, PAGE_TOKENS, dim) or tuple(v_cache.shape[1:]) != (G, PAGE_TOKENS, vd):
+            raise KernelError("sink_attn_prep: the cache pages do not have the head sizes")
+    _chk(cos_v, "value rotation table", torch.float32, 2)
+    if cos_v.shape[1] != vd // 2 or (rot and (cos_k is None or cos_k.shape[1] != rot // 2)):
+        raise KernelError("sink_attn_prep: the rotation tables do not fit")
+    call("mynah_sink_attn_prep", ptr(qkv), qkv.stride(0), code(qkv.dtype), ptr(q_out), ptr(k_cache), ptr(v_cache),
+         ptr(cos_k), ptr(sin_k), cos_k.shape[0] if cos_k is not None else 0, ptr(cos_v), ptr(sin_v), cos_v.shape[0],
+         ptr(ctx.tok_seq), ptr(ctx.tok_pos), ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
+         qkv.shape[0], H, G, dim, vd, rot, 1 if interleaved else 0, ptr(ctx.status), stream_ptr())
+
+
+def sink_attn(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, talk: torch.Tensor,
+              sink: torch.Tensor, cos_v: torch.Tensor, sin_v: torch.Tensor, ctx, pages: PageTableView, H: int, G: int,
+              dim: int, vd: int, window: int, scale: float, interleaved: bool) -> None:
+    """Windowed softmax attention whose denominator holds exp(sink_h), whose heads' weights are mixed by talk [H, H]
+    after the softmax, and whose values are rotated in the cache and turned back at the query (csrc/sink_attn.cu)."""
+    _chk(q, "q", dim=2)
+    _chk(out, "attention output", q.dtype, 2)
+    _chk(talk, "head mixing matrix", dim=2)
+    _chk(sink, "sinks", talk.dtype, 1)
+    if tuple(talk.shape) != (H, H) or sink.numel() != H or q.shape[1] != H * dim or out.shape[1] != H * vd:
+        raise KernelError("sink_attn: sizes do not fit")
+    call("mynah_sink_attn", ptr(q), ptr(out), code(q.dtype), ptr(k_cache), ptr(v_cache), ptr(talk), ptr(sink),
+         code(talk.dtype), ptr(cos_v), ptr(sin_v), cos_v.shape[0], ptr(ctx.tok_seq), ptr(ctx.tok_pos), ptr(pages.indptr),
+         ptr(pages.ids), ptr(pages.base), pages.n_pages, q.shape[0], H, G, dim, vd, int(window or 0), float(scale),
+         1 if interleaved else 0, ptr(ctx.status), stream_ptr())

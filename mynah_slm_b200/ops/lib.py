@@ -105,9 +105,19 @@ _SIGNATURES: dict[str, list] = {
                              P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_int, P, P, P],
     "mynah_selective_scan": [P, c_int, P, c_int, P, c_int, c_int, P, c_int, P, P, c_int, c_int,
                              P, P, P, c_int, P, c_int, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
-    "mynah_delta_prep": [P, c_int, P, P, c_int, c_int, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, P],
-    "mynah_delta_rule": [P, P, P, c_int, c_int, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, P],
-    "mynah_gated_rmsnorm": [P, P, c_int, c_int, P, c_int, P, c_int, c_int, c_int, c_float, P],
+    "mynah_delta_prep": [P, c_int, P, P, c_int, c_int, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, P, c_int, P],
+    "mynah_delta_rule": [P, P, P, c_int, c_int, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P],
+    "mynah_gated_rmsnorm": [P, P, c_int, c_int, P, c_int, P, c_int, c_int, c_int, c_float, c_int, P],
+    "mynah_rmsnorm_add": [P, P, P, P, c_int, c_float, P, c_int, c_float, P, c_int, c_int, P],
+    "mynah_rms_pair_mean": [P, P, P, P, c_int, c_float, c_float, P, c_int, c_int, P],
+    "mynah_rglru_in": [P, c_int, c_int, c_int, c_int, P, P, c_int, P, P, c_int, c_int, P],
+    "mynah_rglru_gates": [P, P, P, c_int, P, P, P, c_int, c_float, P, P, c_int, c_int, c_int, P],
+    "mynah_rglru_scan": [P, P, P, c_int, P, c_int, P, P, P, c_int, c_int, P],
+    "mynah_sink_attn_prep": [P, c_int, c_int, P, P, P, P, P, c_int, P, P, c_int, P, P, P, P, P, c_int,
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+    "mynah_sink_attn": [P, P, c_int, P, P, P, P, c_int, P, P, c_int, P, P, P, P, P, c_int,
+                        c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P, P],
+    "mynah_moe_router_ffn": [P, c_int, P, P, P, c_int, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_scale_f32": [P, c_longlong, c_float, P],
     "mynah_rope_table_freqs": [P, P, c_int, c_int, P, c_double, P],
     "mynah_latent_prep": [P, c_int, c_int, P, c_int, c_int, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -45,6 +45,8 @@ class TensorSpec:
       "table"   integer table: int32
     init decides how the random-weights writer fills it: "normal" is
     N(0, std), "gain" is 1 + N(0, std), "zeros" is all zero.
+    A size of -1 in `shape` is left to the checkpoint (the part reads it off the
+    bound tensor); the random-weights writer then uses `free_size`.
     """
     name: str
     shape: tuple[int, ...]
@@ -52,6 +54,7 @@ class TensorSpec:
     init: str = "normal"
     std: float = 0.02
     ignorable: bool = False      # tolerated in the checkpoint but never read (a stored copy of a tied matrix)
+    free_size: int = 0           # what the random-weights writer puts for a size of -1
 
 
 # ------------------------------------------------------------ cache requests
@@ -223,6 +226,11 @@ class Residual:
         if self.pending is not None:
             self.flush()
         self.pending, self.pending_scale = delta, float(scale)
+
+    def add_f32(self, delta: torch.Tensor) -> None:
+        """Add fp32 rows now (after any pending delta): a sum that must not pass through the activation type."""
+        from ..ops import kernels
+        kernels.residual_add(self.flush(), delta, 1.0)
 
     def take_pending(self):
         """(delta, scale) of the add that is still to be done, which the caller now owes; (None, 1.0) if none."""

@@ -13,12 +13,21 @@ With h the mixer's input (`csrc/delta_rule.cu` states the formulas):
 Head h reads q/k head h // (heads / kv_heads). S (fp32, [heads, dim, vdim]) and
 the convolutions' last taps-1 inputs are the sequence's state.
 
+Variants, chosen by parameters:
+  decay "channel"   one decay a head AND key channel: W_a has heads x dim rows, dt_bias heads x dim values
+                    (A_log stays one a head), and g multiplies the rows of S: S <- diag(g) S
+  gate_act          "silu" (default) or "sigmoid"
+  a_in, g_in        names of a first, narrow matrix: the decay's input is then W_a (W_a_in h) and the gate's
+                    W_g (W_g_in h). The narrow size is `a_rank` / `g_rank` when given, else whatever the
+                    checkpoint's tensors have (the two matrices of a pair must agree)
+
 The six projections of h run as one product (their matrices stacked at bind
 time, padded to a multiple of 8 rows), the three convolutions as one launch over
 the stacked channels.
 
-Parameters: hidden_size, heads, kv_heads, dim, vdim, conv (taps), eps, and the
-tensors' names: q, k, v, q_conv, k_conv, v_conv, b, a, A_log, dt_bias, g, norm, o.
+Parameters: hidden_size, heads, kv_heads, dim, vdim, conv (taps), eps, decay,
+gate_act, a_rank, g_rank, and the tensors' names: q, k, v, q_conv, k_conv,
+v_conv, b, a, A_log, dt_bias, g, norm, o, and optionally a_in, g_in.
 """
 from __future__ import annotations
 
@@ -42,33 +51,72 @@ class GatedDelta(Mixer):
                                                                g("vdim"), g("conv"))
         self.eps = float(spec["eps"])
         self.names = {k: str(spec[k]) for k in _NAMES}
+        for k in ("a_in", "g_in"):
+            self.names[k] = str(spec[k]) if spec.get(k) else None
+        self.channel_decay = spec.get("decay", "head") == "channel"
+        self.gate_act = str(spec.get("gate_act", "silu"))
+        rank = lambda k: -1 if spec.get(k) in (None, "from_checkpoint") else int(spec[k])
+        self.a_rank, self.g_rank = rank("a_rank"), rank("g_rank")
+        if spec.get("decay", "head") not in ("head", "channel"):
+            raise ConfigError(f"gated_delta: decay {spec.get('decay')!r} is neither 'head' nor 'channel'")
+        if self.gate_act not in ("silu", "sigmoid"):
+            raise ConfigError(f"gated_delta: gate activation {self.gate_act!r} is neither 'silu' nor 'sigmoid'")
         if self.H % self.G:
             raise ConfigError(f"gated_delta: {self.H} heads are not a multiple of {self.G} q/k heads")
         if self.dim > 512:
             raise ConfigError(f"gated_delta: keys of {self.dim} values exceed the 512 that the recurrence kernel stages")
+        if self.channel_decay != bool(self.names["a_in"]):
+            raise ConfigError("gated_delta: a decay per channel, and only that, is built from a narrow projection (a_in)")
         self.n_qk = 2 * self.G * self.dim
         self.n_conv = self.n_qk + self.H * self.vd
+        self.n_decay = self.H * self.dim if self.channel_decay else self.H
 
     def tensor_specs(self) -> list[TensorSpec]:
         n, D, H, G, dim, vd, t = self.names, self.D, self.H, self.G, self.dim, self.vd, self.taps
-        return [TensorSpec(n["q"], (G * dim, D)), TensorSpec(n["k"], (G * dim, D)), TensorSpec(n["v"], (H * vd, D)),
-                TensorSpec(n["q_conv"], (G * dim, t), init="normal", std=0.3),
-                TensorSpec(n["k_conv"], (G * dim, t), init="normal", std=0.3),
-                TensorSpec(n["v_conv"], (H * vd, t), init="normal", std=0.3),
-                TensorSpec(n["b"], (H, D)), TensorSpec(n["a"], (H, D)),
-                TensorSpec(n["A_log"], (H,), role="gain", init="normal", std=0.5),
-                TensorSpec(n["dt_bias"], (H,), role="gain", init="normal", std=0.5),
-                TensorSpec(n["g"], (H * vd, D)),
-                TensorSpec(n["norm"], (vd,), role="gain", init="gain", std=0.1),
-                TensorSpec(n["o"], (D, H * vd))]
+        specs = [TensorSpec(n["q"], (G * dim, D)), TensorSpec(n["k"], (G * dim, D)), TensorSpec(n["v"], (H * vd, D)),
+                 TensorSpec(n["q_conv"], (G * dim, t), init="normal", std=0.3),
+                 TensorSpec(n["k_conv"], (G * dim, t), init="normal", std=0.3),
+                 TensorSpec(n["v_conv"], (H * vd, t), init="normal", std=0.3),
+                 TensorSpec(n["b"], (H, D)),
+                 TensorSpec(n["A_log"], (H,), role="gain", init="normal", std=0.5),
+                 TensorSpec(n["dt_bias"], (self.n_decay,), role="gain", init="normal", std=0.5),
+                 TensorSpec(n["norm"], (vd,), role="gain", init="gain", std=0.1),
+                 TensorSpec(n["o"], (D, H * vd))]
+        if n["a_in"]:
+            specs += [TensorSpec(n["a_in"], (self.a_rank, D), free_size=16), TensorSpec(n["a"], (self.n_decay, self.a_rank), std=0.2, free_size=16)]
+        else:
+            specs.append(TensorSpec(n["a"], (self.n_decay, D)))
+        if n["g_in"]:
+            specs += [TensorSpec(n["g_in"], (self.g_rank, D), free_size=16), TensorSpec(n["g"], (H * vd, self.g_rank), std=0.2, free_size=16)]
+        else:
+            specs.append(TensorSpec(n["g"], (H * vd, D)))
+        return specs
 
     def bind(self, tensors: Mapping[str, torch.Tensor], runtime) -> None:
         n = self.names
-        parts = [tensors[n[k]] for k in ("q", "k", "v", "g", "b", "a")]
-        rows = sum(p.shape[0] for p in parts)
-        if rows % 8:
-            parts.append(torch.zeros((8 - rows % 8, self.D), dtype=parts[0].dtype, device=parts[0].device))
+        # the projections of h, stacked: q, k, v, then the gate's (or its narrow matrix), beta's, the decay's (or its
+        # narrow matrix); every piece starts at a multiple of 8 rows, so that a column slice of the product is aligned
+        pieces = [("qkv", torch.cat([tensors[n[k]] for k in ("q", "k", "v")], dim=0)),
+                  ("g", tensors[n["g_in"] or n["g"]]), ("b", tensors[n["b"]]), ("a", tensors[n["a_in"] or n["a"]])]
+        self.at: dict[str, tuple[int, int]] = {}
+        parts, row = [], 0
+        for name, w in pieces:
+            self.at[name] = (row, row + w.shape[0])
+            parts.append(w)
+            row += w.shape[0]
+            if row % 8:
+                parts.append(torch.zeros((8 - row % 8, self.D), dtype=w.dtype, device=w.device))
+                row += 8 - row % 8
         self.w_all = torch.cat(parts, dim=0).contiguous()
+        self.w_a = self.w_g = None
+        if n["a_in"]:
+            if tensors[n["a"]].shape[1] != tensors[n["a_in"]].shape[0]:
+                raise ConfigError(f"gated_delta: {n['a_in']} and {n['a']} do not agree on the narrow size")
+            self.w_a = tensors[n["a"]].contiguous()
+        if n["g_in"]:
+            if tensors[n["g"]].shape[1] != tensors[n["g_in"]].shape[0]:
+                raise ConfigError(f"gated_delta: {n['g_in']} and {n['g']} do not agree on the narrow size")
+            self.w_g = tensors[n["g"]].contiguous()
         self.conv_w = torch.cat([tensors[n["q_conv"]], tensors[n["k_conv"]], tensors[n["v_conv"]]], dim=0).contiguous()
         self.A_log = tensors[n["A_log"]]
         self.dt_bias = tensors[n["dt_bias"]].to(self.A_log.dtype)
@@ -77,7 +125,7 @@ class GatedDelta(Mixer):
         self.act_dtype = runtime.act_dtype
 
     def streamed_tensors(self) -> list:
-        return [self.w_all, self.w_o]
+        return [t for t in (self.w_all, self.w_a, self.w_g, self.w_o) if t is not None]
 
     def state_request(self):
         req = {"S": StateRequest((self.H, self.dim, self.vd), torch.float32)}
@@ -88,13 +136,18 @@ class GatedDelta(Mixer):
     def forward(self, h: torch.Tensor, ctx, cache: CacheView) -> torch.Tensor:
         H, G, dim, vd = self.H, self.G, self.dim, self.vd
         p = kernels.linear(h, self.w_all)
-        c0 = self.n_conv
-        c1 = c0 + H * vd
-        qkv = kernels.causal_conv(p[:, :c0], self.conv_w, None, cache.state.get("conv"), ctx, self.act_dtype, act="silu")
-        qn, kn, g, beta = kernels.delta_prep(qkv[:, : self.n_qk], p[:, c1 + H: c1 + 2 * H], p[:, c1: c1 + H],
-                                             self.A_log, self.dt_bias, H, G, dim)
-        o = kernels.delta_rule(qn, kn, qkv[:, self.n_qk:], g, beta, cache.state["S"], ctx, H, G, dim, vd)
-        out = kernels.gated_rmsnorm(o, p[:, c0:c1], self.norm_w, H, vd, self.eps)
+        col = lambda name: p[:, self.at[name][0]: self.at[name][1]]
+        qkv = kernels.causal_conv(col("qkv"), self.conv_w, None, cache.state.get("conv"), ctx, self.act_dtype, act="silu")
+        gate = col("g") if self.w_g is None else kernels.linear(col("g"), self.w_g)
+        if self.w_a is None:
+            qn, kn, g, beta = kernels.delta_prep(qkv[:, : self.n_qk], col("a"), col("b"), self.A_log, self.dt_bias, H, G, dim)
+        else:
+            a = kernels.linear(col("a"), self.w_a, out_dtype=torch.float32)       # the decay's input is not rounded
+            qn, kn, g, beta = kernels.delta_prep(qkv[:, : self.n_qk], None, col("b"), self.A_log, self.dt_bias, H, G, dim,
+                                                 a_channels=a)
+        o = kernels.delta_rule(qn, kn, qkv[:, self.n_qk:], g, beta, cache.state["S"], ctx, H, G, dim, vd,
+                               channel_decay=self.channel_decay)
+        out = kernels.gated_rmsnorm(o, gate, self.norm_w, H, vd, self.eps, gate_act=self.gate_act)
         return kernels.linear(out, self.w_o, out_dtype=torch.float32)      # unrounded into the norm that follows
 
 

@@ -1,5 +1,6 @@
-"""Feed-forward of several small experts, of which every token uses `top`, picked
-without a router: a table [vocab, top] gives each token id its experts (the
+"""Feed-forwards of several small experts, of which every token uses `top`.
+
+`table_routed_experts` picks without a router: a table [vocab, top] gives each token id its experts (the
 entries of a row differ), and each counts 1/top.
 
 An expert, with h its input (no biases):
@@ -14,6 +15,17 @@ experts' matrices are stacked at bind time.
 Parameters: hidden_size, intermediate_size (of one expert), experts, top, limit,
 alpha (1.702 unless given), vocab_size, table (tensor name) and expert_prefix:
 expert e's tensors are `<expert_prefix><e>.gate`, `.up` and `.down`.
+
+`router_experts` picks with a learned router:
+
+  z = W_r h + b_r  (fp32);  the `top` largest z (the lower index wins a tie);
+  their weights are softmax over the chosen z alone
+  expert:  out = W_down act(W_up h),  act the exact (erf) GELU, no gate, no biases
+  result = sum over the chosen of weight * expert(h),  fp32 rows (not rounded to the activation type)
+
+Parameters: hidden_size, intermediate_size, experts, top, activation
+("gelu_erf"), router, router_bias (tensor names) and expert_prefix: expert e's
+tensors are `<expert_prefix><e>.up` and `.down`.
 """
 from __future__ import annotations
 
@@ -65,3 +77,43 @@ class TableRoutedExperts(FeedForward):
 
 
 register_ffn("table_routed_experts", TableRoutedExperts)
+
+
+class RouterExperts(FeedForward):
+    def __init__(self, spec):
+        super().__init__(spec)
+        g = lambda k: int(spec[k])
+        self.D, self.F, self.E, self.top = g("hidden_size"), g("intermediate_size"), g("experts"), g("top")
+        self.router_name, self.bias_name = str(spec["router"]), str(spec["router_bias"])
+        self.prefix = str(spec["expert_prefix"])
+        if spec.get("activation", "gelu_erf") != "gelu_erf":
+            raise ConfigError(f"router_experts: activation {spec.get('activation')!r} is not built in (gelu_erf)")
+        if not 1 <= self.top <= self.E:
+            raise ConfigError(f"router_experts: top {self.top} does not fit {self.E} experts")
+        if self.E > 1024:
+            raise ConfigError(f"router_experts: {self.E} experts exceed the 1024 that the routing kernel counts")
+
+    def _name(self, e: int, which: str) -> str:
+        return f"{self.prefix}{e}.{which}"
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        specs = [TensorSpec(self.router_name, (self.E, self.D), std=0.3),
+                 TensorSpec(self.bias_name, (self.E,), role="gain", init="normal", std=0.3)]
+        for e in range(self.E):
+            specs += [TensorSpec(self._name(e, "up"), (self.F, self.D)), TensorSpec(self._name(e, "down"), (self.D, self.F))]
+        return specs
+
+    def bind(self, tensors: Mapping[str, torch.Tensor], runtime) -> None:
+        self.w_router = tensors[self.router_name].contiguous()
+        self.b_router = tensors[self.bias_name].contiguous()
+        self.w_up = torch.stack([tensors[self._name(e, "up")] for e in range(self.E)]).contiguous()
+        self.w_down = torch.stack([tensors[self._name(e, "down")] for e in range(self.E)]).contiguous()
+
+    def streamed_tensors(self) -> list:
+        return [self.w_router]          # of the experts a step reads only those its tokens pick
+
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        return kernels.moe_router_ffn(h, self.w_router, self.b_router, self.w_up, self.w_down, ctx, self.top)
+
+
+register_ffn("router_experts", RouterExperts)

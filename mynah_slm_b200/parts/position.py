@@ -17,7 +17,12 @@ optionally the interpolation for contexts longer than the trained one
 dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i
 turns at f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are both
 multiplied by 0.1 ln(factor) + 1. Frequencies are made in double on the host,
-angles in double on the device; the tables are float.
+angles in double on the device; the tables are float. A second form of
+scaling, `kind: "wavelength"` (factor, low, high, original), goes by each pair's
+wavelength l_i = 2 pi / f_i: pairs with l_i < original / high keep f_i, pairs
+with l_i > original / low turn at f_i / factor, and between the two, with
+s = (original / l_i - low) / (high - low), at (1 - s) f_i / factor + s f_i;
+cos and sin keep their size.
 
 `none`: no position encoding (the mixer then only norms and stores).
 """
@@ -62,6 +67,19 @@ def rotary_frequencies(dims: int, base: float, scaling=None) -> tuple[list[float
     if not scaling:
         return f, 1.0
     factor, original = float(scaling["factor"]), float(scaling["original"])
+    if scaling.get("kind") == "wavelength":
+        low, high = float(scaling["low"]), float(scaling["high"])
+        out = []
+        for fi in f:
+            wavelength = 2.0 * math.pi / fi
+            if wavelength < original / high:
+                out.append(fi)
+            elif wavelength > original / low:
+                out.append(fi / factor)
+            else:
+                s = (original / wavelength - low) / (high - low)
+                out.append((1.0 - s) * fi / factor + s * fi)
+        return out, 1.0
 
     def at(turns: float) -> float:
         return dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
@@ -76,8 +94,8 @@ def rotary_frequencies(dims: int, base: float, scaling=None) -> tuple[list[float
 
 
 class Rotary(PositionEncoding):
-    """Parameters: dims, base, pairing ("half" | "interleaved"), scaling (None or a mapping with factor,
-    original, fast, slow)."""
+    """Parameters: dims, base, pairing ("half" | "interleaved"), scaling (None, or a mapping with factor,
+    original, fast, slow, or one with kind "wavelength", factor, original, low, high)."""
     fusable = True
 
     def __init__(self, spec):
@@ -87,20 +105,25 @@ class Rotary(PositionEncoding):
         self.base = float(spec["base"])
         self.pairing = str(spec.get("pairing", "half"))
         sc = spec.get("scaling")
-        self.scaling = {k: float(sc[k]) for k in ("factor", "original", "fast", "slow")} if sc else None
+        self.scaling = None
+        if sc and sc.get("kind") == "wavelength":
+            self.scaling = {"kind": "wavelength", **{k: float(sc[k]) for k in ("factor", "original", "low", "high")}}
+            if self.scaling["low"] == self.scaling["high"]:
+                raise ConfigError("rotary: the wavelength scaling's low and high are equal")
+        elif sc:
+            self.scaling = {k: float(sc[k]) for k in ("factor", "original", "fast", "slow")}
         if self.dims <= 0 or self.dims % 2:
             raise ConfigError(f"rotary: dims {self.dims} must be positive and even")
         if self.pairing not in ("half", "interleaved"):
             raise ConfigError(f"rotary: pairing {self.pairing!r} is neither 'half' nor 'interleaved'")
-        if not self.base > 0.0 or (self.scaling and not (self.scaling["factor"] > 0.0 and self.scaling["original"] > 0.0
-                                                         and self.scaling["fast"] > 0.0 and self.scaling["slow"] > 0.0)):
+        if not self.base > 0.0 or (self.scaling and not all(v > 0.0 for v in self.scaling.values() if not isinstance(v, str))):
             raise ConfigError("rotary: base and the scaling's constants must be positive")
         self.interleaved = self.pairing == "interleaved"
         self.cos: Optional[torch.Tensor] = None
         self.sin: Optional[torch.Tensor] = None
 
     def prepare(self, runtime) -> None:
-        key = ("rotary", self.dims, self.base, tuple(sorted(self.scaling.items())) if self.scaling else None)
+        key = ("rotary", self.dims, self.base, tuple(sorted(self.scaling.items(), key=lambda kv: kv[0])) if self.scaling else None)
         if key not in runtime.tables:
             freqs, mult = rotary_frequencies(self.dims, self.base, self.scaling)
             runtime.tables[key] = kernels.rope_table_freqs(runtime.max_positions, freqs, mult, runtime.device)

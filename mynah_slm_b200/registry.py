@@ -88,6 +88,8 @@ def _register_builtin() -> None:
     register_architecture(supisun.ARCHITECTURE, supisun.SupisunConfig.from_dict, replace=True)
     from .config import nedupel
     register_architecture(nedupel.ARCHITECTURE, nedupel.NedupelConfig.from_dict, replace=True)
+    from .config import gupizen
+    register_architecture(gupizen.ARCHITECTURE, gupizen.GupizenConfig.from_dict, replace=True)
 
 
 _register_builtin()

@@ -51,7 +51,7 @@ def kept_dtype(role: str, stored: torch.dtype, run_dtype: torch.dtype) -> torch.
 def check(specs: list[tuple[Part, TensorSpec]], ckpt: Checkpoint) -> None:
     wanted: dict[str, TensorSpec] = {}
     for _, ts in specs:
-        if ts.name in wanted and wanted[ts.name].shape != ts.shape:
+        if ts.name in wanted and tuple(wanted[ts.name].shape) != tuple(ts.shape):
             raise ValueError(f"two parts ask for {ts.name} with different shapes")
         if ts.name not in wanted or not ts.ignorable:
             wanted[ts.name] = ts
@@ -62,7 +62,7 @@ def check(specs: list[tuple[Part, TensorSpec]], ckpt: Checkpoint) -> None:
     for n, ts in wanted.items():
         if n in have and not ts.ignorable:
             e = have[n]
-            if tuple(e.shape) != tuple(ts.shape):
+            if len(e.shape) != len(ts.shape) or any(w != -1 and int(g) != w for g, w in zip(e.shape, ts.shape)):
                 wrong_shape.append((n, e.shape, ts.shape))
             is_float = e.dtype in ("F32", "BF16", "F16", "F64")
             if (ts.role == "table") == is_float:

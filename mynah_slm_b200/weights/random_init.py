@@ -19,6 +19,7 @@ written and read back.
 """
 from __future__ import annotations
 
+import dataclasses
 import json
 import os
 
@@ -71,8 +72,17 @@ def _wanted(model: Model) -> list[TensorSpec]:
         if ts.ignorable or ts.name in seen:
             continue
         seen.add(ts.name)
-        out.append(ts)
+        out.append(_sized(ts))
     return out
+
+
+def _sized(ts: TensorSpec) -> TensorSpec:
+    """A size that the checkpoint would give (-1) is the writer's own choice: the part's `free_size`."""
+    if all(d != -1 for d in ts.shape):
+        return ts
+    if ts.free_size < 1:
+        raise ValueError(f"{ts.name}: a size is left to the checkpoint and the part names none for random weights")
+    return dataclasses.replace(ts, shape=tuple(ts.free_size if d == -1 else d for d in ts.shape))
 
 
 def host_tensor(ts: TensorSpec, seed: int, dtype: torch.dtype) -> torch.Tensor:
@@ -144,7 +154,7 @@ def fill_into(parts_and_specs, source: RandomWeights, runtime) -> None:
         if ts.ignorable:
             continue
         if ts.name not in made:
-            t = device_tensor(ts, source.seed, source.stored_dtype, runtime.device)
+            t = device_tensor(_sized(ts), source.seed, source.stored_dtype, runtime.device)
             made[ts.name] = t.to(kept_dtype(ts.role, t.dtype, runtime.act_dtype))
         entry[1][ts.name] = made[ts.name]
     for part, tensors in by_part.values():
