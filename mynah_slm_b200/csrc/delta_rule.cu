@@ -71,7 +71,7 @@ delta_prep_kernel(const T* __restrict__ qk, const T* __restrict__ a_raw, const T
 }
 
 constexpr int DELTA_THREADS = 128;
-constexpr int DELTA_TB = 16;                // tokens staged in shared memory at a time
+constexpr int DELTA_TB = 16;                // tokens staged in shared memory at a time (8 where 16 do not fit)
 
 struct DeltaArgs {
     int B, H, G, dim, vd, n_slots, ldv;
@@ -85,7 +85,7 @@ struct DeltaArgs {
 // vectors) from different banks.
 __device__ __forceinline__ int kq_slot(int i, int per, int stride) { return (i / per) * stride + i % per; }
 
-template <typename T, int RMAX, bool CH>
+template <typename T, int RMAX, bool CH, int TB>
 __global__ void __launch_bounds__(2 * DELTA_THREADS)
 delta_rule_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const T* __restrict__ v,
                   const float* __restrict__ g, const float* __restrict__ beta, float* __restrict__ state,
@@ -107,20 +107,20 @@ delta_rule_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
     const int kvh = h / (a.H / a.G);
     constexpr int CS = RMAX + 4;                                 // floats of a lane's chunk
     const int row = CS * L;                                      // floats of a staged key (or query)
-    const int nk = DELTA_TB * row, nv = DELTA_TB * JT;
+    const int nk = TB * row, nv = TB * JT;
     float* ks = sm;                                              // [2][TB][row]
     float* qs = ks + 2 * nk;                                     // [2][TB][row]
     float* vs = qs + 2 * nk;                                     // [2][TB][JT]
     float* os = vs + 2 * nv;                                     // [2][TB][JT]
     float* gs = os + 2 * nv;                                     // [2][2][TB]: decay, beta
-    float* gv = gs + 4 * DELTA_TB;                               // [2][TB][row]: a decay per key channel (CH)
+    float* gv = gs + 4 * TB;                               // [2][TB][row]: a decay per key channel (CH)
     for (int i = threadIdx.x; i < 4 * nk; i += 2 * DELTA_THREADS) ks[i] = 0.f;      // the unused slots stay zero
     if (CH)
         for (int i = threadIdx.x; i < 2 * nk; i += 2 * DELTA_THREADS) gv[i] = 0.f;
     __syncthreads();
 
     auto stage = [&](int k) {                                    // block k of the sequence's rows -> buffer k & 1
-        const int t0 = q0 + k * DELTA_TB, nt = min(DELTA_TB, q1 - t0), buf = k & 1;
+        const int t0 = q0 + k * TB, nt = min(TB, q1 - t0), buf = k & 1;
         if (a.vec) {
             // four consecutive values a load, four loads of k and of q a thread issued before the first is used
             const int d4 = a.dim / 4, total = nt * d4;
@@ -162,12 +162,12 @@ delta_rule_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
             vs[buf * nv + idx] = col < a.vd ? to_f32(v[(size_t)(t0 + tt) * a.ldv + (size_t)h * a.vd + col]) : 0.f;
         }
         if (tid < nt) {
-            gs[buf * 2 * DELTA_TB + tid] = CH ? 1.0f : g[(size_t)(t0 + tid) * a.H + h];
-            gs[buf * 2 * DELTA_TB + DELTA_TB + tid] = beta[(size_t)(t0 + tid) * a.H + h];
+            gs[buf * 2 * TB + tid] = CH ? 1.0f : g[(size_t)(t0 + tid) * a.H + h];
+            gs[buf * 2 * TB + TB + tid] = beta[(size_t)(t0 + tid) * a.H + h];
         }
     };
     auto write_out = [&](int k) {
-        const int t0 = q0 + k * DELTA_TB, nt = min(DELTA_TB, q1 - t0), buf = k & 1;
+        const int t0 = q0 + k * TB, nt = min(TB, q1 - t0), buf = k & 1;
         for (int idx = tid; idx < nt * JT; idx += DELTA_THREADS) {
             const int tt = idx / JT, col = blockIdx.x * JT + idx % JT;
             if (col < a.vd) o[(size_t)(t0 + tt) * a.H * a.vd + (size_t)h * a.vd + col] = os[buf * nv + idx];
@@ -184,15 +184,15 @@ delta_rule_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
         stage(0);
     }
     __syncthreads();
-    const int n_blocks = (q1 - q0 + DELTA_TB - 1) / DELTA_TB;
+    const int n_blocks = (q1 - q0 + TB - 1) / TB;
     for (int k = 0; k < n_blocks; k++) {
         if (stager) {
             if (k + 1 < n_blocks) stage(k + 1);
             if (k > 0) write_out(k - 1);
         } else {
-            const int nt = min(DELTA_TB, q1 - q0 - k * DELTA_TB), buf = k & 1;
+            const int nt = min(TB, q1 - q0 - k * TB), buf = k & 1;
             for (int tt = 0; tt < nt; tt++) {
-                const float gt = gs[buf * 2 * DELTA_TB + tt], bt = gs[buf * 2 * DELTA_TB + DELTA_TB + tt];
+                const float gt = gs[buf * 2 * TB + tt], bt = gs[buf * 2 * TB + TB + tt];
                 const float4* k4 = reinterpret_cast<const float4*>(ks + buf * nk + tt * row + l * CS);
                 const float4* q4 = reinterpret_cast<const float4*>(qs + buf * nk + tt * row + l * CS);
                 float kr[RMAX];
@@ -316,12 +316,20 @@ MYNAH_API int mynah_delta_rule(const float* qn, const float* kn, const void* v, 
     const int JT = DELTA_THREADS / L;
     const dim3 grid(ceil_div(vd, JT), H, B);
     const int rmax = per <= 16 ? 16 : 32;
-    const size_t smem = sizeof(float) * ((size_t)(channel_decay ? 6 : 4) * DELTA_TB * (rmax + 4) * L + (size_t)4 * DELTA_TB * JT + 4 * DELTA_TB);
+    auto smem_for = [&](int tb) {
+        return sizeof(float) * ((size_t)(channel_decay ? 6 : 4) * tb * (rmax + 4) * L + (size_t)4 * tb * JT + 4 * tb);
+    };
+    // a decay per channel is staged like a third key: with the longest keys only half as many tokens fit
+    const int tb = smem_for(DELTA_TB) <= 200 * 1024 ? DELTA_TB : DELTA_TB / 2;
+    const size_t smem = smem_for(tb);
 #define DELTA_LAUNCH(T, RMAX, CH)                                                                                      \
+    if (tb == DELTA_TB) { DELTA_LAUNCH_TB(T, RMAX, CH, DELTA_TB); }                                                    \
+    else { DELTA_LAUNCH_TB(T, RMAX, CH, DELTA_TB / 2); }
+#define DELTA_LAUNCH_TB(T, RMAX, CH, TB)                                                                                   \
     if (smem > 48 * 1024 &&                                                                                            \
-        cudaFuncSetAttribute(delta_rule_kernel<T, RMAX, CH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
+        cudaFuncSetAttribute(delta_rule_kernel<T, RMAX, CH, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
         return mynah_fail("delta_rule: %zu bytes of shared memory are not to be had", smem);                          \
-    mynah_launch(delta_rule_kernel<T, RMAX, CH>, grid, dim3(2 * DELTA_THREADS), smem, stream, qn, kn, (const T*)v, g, beta, state, o, \
+    mynah_launch(delta_rule_kernel<T, RMAX, CH, TB>, grid, dim3(2 * DELTA_THREADS), smem, stream, qn, kn, (const T*)v, g, beta, state, o, \
                  cu_q, slots, a)
 #define DELTA_LAUNCH_R(T, CH)                  \
     if (rmax == 16) { DELTA_LAUNCH(T, 16, CH); } \
@@ -335,6 +343,7 @@ MYNAH_API int mynah_delta_rule(const float* qn, const float* kn, const void* v, 
         else { DELTA_LAUNCH_R(bf16, false); }
     }
 #undef DELTA_LAUNCH_R
+#undef DELTA_LAUNCH_TB
 #undef DELTA_LAUNCH
     return mynah_check_launch("delta_rule");
 }
