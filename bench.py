@@ -7,6 +7,7 @@ and 64.
     python bench.py --workload 4b|8b      (the two larger workloads, a JSON line of their own each)
     python bench.py --design supisun      (the Supisun design beside Qwen3 at equal size, a JSON line of its own)
     python bench.py --design nedupel      (the Nedupel design beside Supisun and Qwen3 at equal size, likewise)
+    python bench.py --design gupizen      (the Gupizen design beside Supisun, Nedupel and Qwen3 at equal size, likewise)
 
 One JSON line on stdout. A step is one decode step of the batch.
   value     decoded tokens per second, timed on the device with CUDA events
@@ -338,6 +339,27 @@ def nedupel_config(shape: str, layers: int) -> dict:
             "residual_mult": 0.7, "logit_scale": 0.25, "norm": {"eps": 1e-6}, "layers": out}
 
 
+# The Gupizen design at layer sizes that resemble a real model's, beside Supisun (the closest existing design: windowed
+# attention, a delta rule and input convolutions), Nedupel (routed experts) and Qwen3 at equal width, depth, heads and
+# vocabulary. Its layers repeat (parallel, parallel, channel delta); the attention keeps the Qwen3 shape's heads with a
+# window of 1,024 positions, the recurrent unit beside it has the model's width in as many blocks as heads; every layer
+# has 16 experts of half the dense width of which a token uses 2.
+def gupizen_config(shape: str, layers: int) -> dict:
+    c = dict(QWEN3_0_6B)
+    c.update(SHAPES[shape])
+    D, H, G, HD, F = c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"], c["intermediate_size"]
+    moe = {"kind": "moe", "expert": {"ff": F // 2}, "router": {"experts": 16, "top": 2}}
+    par = {"type": "parallel", "mlp": moe, "mixer": {
+        "left": {"heads": H, "kv_heads": G, "dim": HD, "vdim": HD, "scale": HD ** -0.5, "mask": {"size": 1024},
+                 "rot": {"dims": HD // 2, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}},
+        "right": {"width": D, "blocks": H, "conv": 4}}}
+    dlt = {"type": "channel_delta", "mlp": moe, "mixer": {"heads": H, "kv_heads": G, "dim": HD, "vdim": HD, "conv": 4,
+                                                         "decay_rank": 64, "gate_rank": 64}}
+    pattern = [par, par, dlt]
+    return {"architecture": "Gupizen", "vocab": c["vocab_size"], "width": D, "max_positions": 8192, "norm": {"eps": 1e-6},
+            "canon": {"taps": 3}, "embedding": {"scale": D ** 0.5}, "layers": [pattern[i % 3] for i in range(layers)]}
+
+
 def run_design(args) -> int:
     """`--design NAME`: prefill of one 2,048-token prompt and decode steps at --batch behind 2,048-token prompts, for
     the design and for the existing models at equal size (`--model` runs one of them: for a launch list of that model alone)."""
@@ -360,8 +382,10 @@ def run_design(args) -> int:
         q["num_hidden_layers"] = layers
         res = {"layers": layers}
         arms = [("supisun", supisun_config(shape, layers)), ("qwen3", q)]
-        if args.design == "nedupel":
+        if args.design in ("nedupel", "gupizen"):
             arms.insert(0, ("nedupel", nedupel_config(shape, layers)))
+        if args.design == "gupizen":
+            arms.insert(0, ("gupizen", gupizen_config(shape, layers)))
         for name, cfg in arms:
             if args.model and args.model != name:
                 continue
@@ -469,9 +493,9 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of the decode phases")
     ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes, for --only runs (the full line is always 0.6b)")
     ap.add_argument("--workload", default="", choices=["", "4b", "8b"], help="run one of the two larger workloads instead")
-    ap.add_argument("--design", default="", choices=["", "supisun", "nedupel"],
+    ap.add_argument("--design", default="", choices=["", "supisun", "nedupel", "gupizen"],
                     help="measure this design beside Qwen3 at equal size instead (prefill and decode; a line of its own)")
-    ap.add_argument("--model", default="", choices=["", "supisun", "nedupel", "qwen3"], help="with --design: only this one of the models")
+    ap.add_argument("--model", default="", choices=["", "supisun", "nedupel", "gupizen", "qwen3"], help="with --design: only this one of the models")
     args = ap.parse_args()
 
     if args.impl == "reference":
