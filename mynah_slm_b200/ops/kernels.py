@@ -1141,3 +1141,38 @@ def sink_attn(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
          code(talk.dtype), ptr(cos_v), ptr(sin_v), cos_v.shape[0], ptr(ctx.tok_seq), ptr(ctx.tok_pos), ptr(pages.indptr),
          ptr(pages.ids), ptr(pages.base), pages.n_pages, q.shape[0], H, G, dim, vd, int(window or 0), float(scale),
          1 if interleaved else 0, ptr(ctx.status), stream_ptr())
+
+
+def sink_attn_tc_supported(dtype: torch.dtype, H: int, G: int, dim: int, vd: int) -> bool:
+    return dtype == torch.bfloat16 and bool(lib.load().mynah_sink_attn_tc_supported(H, G, dim, vd))
+
+
+def sink_attn_tc_scratch(T: int, H: int, vd: int, splits: int) -> int:
+    """fp32 words of scratch: log2 of the denominators [T, H], and the shares' partial sums when there are several."""
+    return T * H + (splits * T * H * vd if splits > 1 else 0)
+
+
+def sink_attn_tc(q: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 talk: torch.Tensor, sink: torch.Tensor, cos_v: torch.Tensor, sin_v: torch.Tensor, ctx, pages: PageTableView,
+                 H: int, G: int, dim: int, vd: int, window: int, scale: float, interleaved: bool, splits: int) -> None:
+    """sink_attn on tensor cores (bfloat16, heads of 64 or 128; csrc/sink_attn_tc.cu): the denominators first, then one
+    pass over the keys that mixes the heads' weights and multiplies with V, the keys in `splits` shares."""
+    _chk(q, "q", torch.bfloat16, 2)
+    _chk(out, "attention output", torch.bfloat16, 2)
+    _chk(talk, "head mixing matrix", dim=2)
+    _chk(sink, "sinks", talk.dtype, 1)
+    _chk(scratch, "scratch", torch.float32, 1)
+    T = q.shape[0]
+    if tuple(talk.shape) != (H, H) or sink.numel() != H or q.shape[1] != H * dim or tuple(out.shape) != (T, H * vd):
+        raise KernelError("sink_attn_tc: sizes do not fit")
+    if k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
+        raise KernelError("sink_attn_tc: the cache is not bfloat16")
+    if tuple(k_cache.shape[1:]) != (G, PAGE_TOKENS, dim) or tuple(v_cache.shape[1:]) != (G, PAGE_TOKENS, vd):
+        raise KernelError("sink_attn_tc: the cache pages do not have the head sizes")
+    if scratch.numel() < sink_attn_tc_scratch(T, H, vd, splits):
+        raise KernelError("sink_attn_tc: scratch too small")
+    part = scratch[T * H:] if splits > 1 else None
+    call("mynah_sink_attn_tc", ptr(q), ptr(out), ptr(scratch), ptr(part), ptr(k_cache), ptr(v_cache), ptr(talk), ptr(sink),
+         code(talk.dtype), ptr(cos_v), ptr(sin_v), cos_v.shape[0], ptr(ctx.cu_q), ptr(ctx.kv_len), ptr(ctx.tok_seq),
+         ptr(ctx.tok_pos), ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, T, ctx.B, H, G, dim, vd,
+         int(window or 0), float(scale), 1 if interleaved else 0, int(splits), ptr(ctx.status), stream_ptr())

@@ -117,6 +117,8 @@ _SIGNATURES: dict[str, list] = {
                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_sink_attn": [P, P, c_int, P, P, P, P, c_int, P, P, c_int, P, P, P, P, P, c_int,
                         c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P, P],
+    "mynah_sink_attn_tc": [P, P, P, P, P, P, P, P, c_int, P, P, c_int, P, P, P, P, P, P, P, c_int, c_int, c_int,
+                           c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, P, P],
     "mynah_moe_router_ffn": [P, c_int, P, P, P, c_int, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_scale_f32": [P, c_longlong, c_float, P],
     "mynah_rope_table_freqs": [P, P, c_int, c_int, P, c_double, P],
@@ -159,6 +161,8 @@ def load() -> ctypes.CDLL:
     lib.mynah_gemm_qkv_rope_supported.argtypes = [c_int, c_int, c_int, c_int, c_int]
     lib.mynah_argmax_parts.restype = c_int
     lib.mynah_argmax_parts.argtypes = []
+    lib.mynah_sink_attn_tc_supported.restype = c_int
+    lib.mynah_sink_attn_tc_supported.argtypes = [c_int, c_int, c_int, c_int]
     lib.mynah_attn_prefill_tc_supported.restype = c_int
     lib.mynah_attn_prefill_tc_supported.argtypes = [c_int, c_int, c_int]
     lib.mynah_attn_prefill_tcgen05_supported.restype = c_int

@@ -80,6 +80,7 @@ class SinkTalkAttention(Mixer):
         self.w_o = tensors[n["o"]]
         self.talk = tensors[n["talk"]].contiguous()
         self.sink = tensors[n["sink"]].to(self.talk.dtype).contiguous()
+        self.runtime = runtime
         self.cos_k = self.sin_k = self.cos_v = self.sin_v = None
         if self.position is not None:
             self.position.prepare(runtime)
@@ -104,6 +105,15 @@ class SinkTalkAttention(Mixer):
         kernels.sink_attn_prep(qkv, q, cache.k if writes else None, cache.v if writes else None, self.cos_k, self.sin_k,
                                self.cos_v, self.sin_v, ctx, pages, H, G, dim, vd, self.rot_dims, self.interleaved)
         out = torch.empty((T, H * vd), dtype=qkv.dtype, device=qkv.device)
+        if kernels.sink_attn_tc_supported(qkv.dtype, H, G, dim, vd) and cache.k.dtype == torch.bfloat16:
+            # a decode step shares a sequence's key tiles among CTAs, one share per page in sight
+            in_sight = ctx.decode_splits if self.window is None else min(ctx.decode_splits, (self.window + 126) // 64 + 1)
+            splits = max(1, in_sight) if ctx.is_decode else 1
+            words = kernels.sink_attn_tc_scratch(T, H, vd, splits)
+            scratch = self.runtime.attn_scratch(1, 1, words, 1)
+            kernels.sink_attn_tc(q, out, scratch, cache.k, cache.v, self.talk, self.sink, self.cos_v, self.sin_v, ctx, pages,
+                                 H, G, dim, vd, self.window or 0, self.scale, self.interleaved, splits)
+            return kernels.linear(out, self.w_o, out_dtype=torch.float32)
         kernels.sink_attn(q, out, cache.k, cache.v, self.talk, self.sink, self.cos_v, self.sin_v, ctx, pages, H, G, dim, vd,
                           self.window or 0, self.scale, self.interleaved)
         return kernels.linear(out, self.w_o, out_dtype=torch.float32)      # unrounded into the norm that follows

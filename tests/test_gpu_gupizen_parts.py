@@ -25,7 +25,7 @@ def rel(ref, got):
     return float(np.abs(ref - got).max() / max(np.abs(ref).max(), 1e-30))
 
 
-def ctx_for(q_lens, slots, starts=None, pad_rows=0, page_lists=None, n_pages=0, bases=None):
+def ctx_for(q_lens, slots, starts=None, pad_rows=0, page_lists=None, n_pages=0, bases=None, decode_splits=1):
     """The fields of a step's context that the parts read: rows packed sequence by sequence, then padding rows."""
     from mynah_slm_b200.ops.kernels import PageTableView
     starts = starts or [0] * len(q_lens)
@@ -41,6 +41,7 @@ def ctx_for(q_lens, slots, starts=None, pad_rows=0, page_lists=None, n_pages=0, 
         indptr = np.cumsum([0] + [len(p) for p in page_lists])
         pages = [PageTableView(i32(indptr), i32([p for l in page_lists for p in l]), i32(bases or [0] * len(q_lens)), n_pages)]
     return SimpleNamespace(tok_seq=i32(tok_seq), tok_pos=i32(tok_pos), cu_q=i32(cu), slots=i32(slots), B=len(q_lens),
+                           kv_len=i32([s + n for n, s in zip(q_lens, starts)]), decode_splits=decode_splits,
                            T=len(tok_seq), status=torch.zeros((1,), dtype=torch.int32, device=DEV), pages=pages,
                            is_decode=all(n == 1 for n in q_lens) and pad_rows == 0, max_q_len=max(q_lens))
 
@@ -163,6 +164,54 @@ def test_sink_attention_in_bfloat16():
     ctx = ctx_for([T], [0], page_lists=[[3, 0, 1]], n_pages=4)
     out = part.forward(h.to(DEV), ctx, cache).cpu().numpy()
     assert rel(ref, out) < 3e-2
+
+
+@pytest.mark.parametrize("H,G,dim,vd,window,splits", [(4, 2, 64, 128, 40, 3), (16, 8, 128, 128, 100, 2), (3, 3, 128, 64, None, 5),
+                                                       (20, 5, 64, 64, 65, 1), (2, 1, 128, 128, 32, 4)])
+def test_sink_attention_on_tensor_cores(monkeypatch, H, G, dim, vd, window, splits):
+    """bfloat16 with heads of 64 or 128 takes the tensor-core kernels: two unequal prompts in one step (with padding
+    rows), a portion of two tokens each, then twenty tokens one by one with the keys in `splits` shares, over pages
+    in no order. Against the general kernel on the same rows (they differ by the output's rounding at most) and
+    against the plain implementation."""
+    from mynah_slm_b200.ops import kernels
+    from mynah_slm_b200.parts import CacheView
+    D, LA, LB, ND = 48, 150, 37, 20
+    m, W, spec = _attention_case(H, G, dim, vd, window or 4096, 32, D, seed=H + dim)
+    if window is None:
+        spec = type(spec)(spec.kind, {**dict(spec.params), "window": None})
+    hA = torch.tensor(np.random.default_rng(5).normal(size=(LA + 2 + ND, D))).to(torch.bfloat16)
+    hB = torch.tensor(np.random.default_rng(6).normal(size=(LB + 2 + ND, D))).to(torch.bfloat16)
+    steps = [((0, LA), (0, LB), 2), ((LA, LA + 2), (LB, LB + 2), 0)] + [((LA + 2 + i, LA + 3 + i), (LB + 2 + i, LB + 3 + i), 0) for i in range(ND)]
+    used = []
+
+    def run(tc):
+        if not tc:
+            monkeypatch.setattr(kernels, "sink_attn_tc_supported", lambda *a: False)
+        else:
+            real = kernels.sink_attn_tc
+            monkeypatch.setattr(kernels, "sink_attn_tc", lambda *a, **k: (used.append(1), real(*a, **k))[1])
+        part = bound("mixer", spec, W, dtype=torch.bfloat16)
+        cache = CacheView(group=0, k=torch.full((9, G, 64, dim), 3.0, dtype=torch.bfloat16, device=DEV),
+                          v=torch.full((9, G, 64, vd), 3.0, dtype=torch.bfloat16, device=DEV), writes=True)
+        outA, outB = [], []
+        for (a0, a1), (b0, b1), pad in steps:
+            ctx = ctx_for([a1 - a0, b1 - b0], [0, 1], starts=[a0, b0], pad_rows=pad, page_lists=[[7, 2, 5], [8, 0]], n_pages=9,
+                          decode_splits=splits)
+            x = torch.cat([hA[a0:a1], hB[b0:b1], torch.zeros((pad, D), dtype=torch.bfloat16)], 0).to(DEV).contiguous()
+            out = part.forward(x, ctx, cache).float().cpu().numpy()
+            assert int(ctx.status.item()) == 0
+            outA.append(out[:a1 - a0])
+            outB.append(out[a1 - a0:a1 - a0 + b1 - b0])
+        monkeypatch.undo()
+        return np.concatenate(outA, 0), np.concatenate(outB, 0)
+
+    tcA, tcB = run(True)
+    assert len(used) == len(steps)
+    gA, gB = run(False)
+    assert rel(gA, tcA) < 6e-3 and rel(gB, tcB) < 6e-3
+    mm = dict(m, mask={"size": window or 10 ** 6})
+    assert rel(plain.sink_talk_attention(hA.to(torch.float64).numpy(), W, mm, np.arange(len(hA))), tcA) < 3e-2
+    assert rel(plain.sink_talk_attention(hB.to(torch.float64).numpy(), W, mm, np.arange(len(hB))), tcB) < 3e-2
 
 
 def _states(req, n_slots):
