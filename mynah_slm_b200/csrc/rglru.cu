@@ -111,6 +111,56 @@ __global__ void rglru_scan_kernel(const float* __restrict__ a, const float* __re
     state[(size_t)slot * width + c] = S;
 }
 
+// The same along long sequences: a CTA takes 32 channels of a sequence and cuts its rows into SCAN_PIECES pieces, a warp
+// each. A piece first runs from zero and keeps the product of its decays, P, and its end value, E (the recurrence is
+// linear: with S entering, the piece ends at P S + E); every warp then folds the pieces before its own in their order
+// and runs its piece again from the state it found. A sequence of fewer than SCAN_LONG rows is one piece, summed in the
+// order of the kernel above; which way a sequence goes depends on its own length alone.
+constexpr int SCAN_PIECES = 32;
+constexpr int SCAN_LONG = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(32 * SCAN_PIECES)
+rglru_scan_pieces_kernel(const float* __restrict__ a, const float* __restrict__ bx, const T* __restrict__ y,
+                         float* __restrict__ state, int n_slots, T* __restrict__ out,
+                         const int* __restrict__ cu_q, const int* __restrict__ slots, int width) {
+    __shared__ float Ps[SCAN_PIECES][32], Es[SCAN_PIECES][32];
+    griddep_wait();
+    const int b = blockIdx.y;
+    const int lane = threadIdx.x, w = threadIdx.y;
+    const int c = blockIdx.x * 32 + lane;
+    const int slot = slots[b];
+    const int q0 = cu_q[b], q1 = cu_q[b + 1];
+    if (slot < 0 || slot >= n_slots || q1 <= q0) return;
+    const int n = q1 - q0;
+    const int per = n < SCAN_LONG ? n : (n + SCAN_PIECES - 1) / SCAN_PIECES;
+    const int t0 = min(q1, q0 + w * per), t1 = min(q1, t0 + per);
+    const bool live = c < width;
+    float P = 1.f, E = 0.f;
+    if (live && n >= SCAN_LONG) {
+#pragma unroll 4
+        for (int t = t0; t < t1; t++) {
+            const size_t at = (size_t)t * width + c;
+            const float av = a[at];
+            P *= av;
+            E = fmaf(av, E, bx[at]);
+        }
+    }
+    Ps[w][lane] = P;
+    Es[w][lane] = E;
+    __syncthreads();
+    if (!live) return;
+    float S = state[(size_t)slot * width + c];
+    for (int j = 0; j < w; j++) S = fmaf(Ps[j][lane], S, Es[j][lane]);
+#pragma unroll 4
+    for (int t = t0; t < t1; t++) {
+        const size_t at = (size_t)t * width + c;
+        S = fmaf(a[at], S, bx[at]);
+        out[at] = from_f32<T>(S * to_f32(y[at]));
+    }
+    if (w == (n - 1) / per) state[(size_t)slot * width + c] = S;   // the last piece that has rows
+}
+
 }  // namespace
 
 MYNAH_API int mynah_rglru_in(const void* p, int ldp, int y_off, int x_off, int dtype, const void* by, const void* bx, int b_dtype,
@@ -155,9 +205,19 @@ MYNAH_API int mynah_rglru_gates(const float* u, const void* ra, const void* ri, 
 
 // a, bx fp32 [T, width]; y, out [T, width] in dtype; state fp32 [n_slots + 1, width].
 MYNAH_API int mynah_rglru_scan(const float* a, const float* bx, const void* y, int dtype, float* state, int n_slots, void* out,
-                               const int* cu_q, const int* slots, int B, int width, cudaStream_t stream) {
+                               const int* cu_q, const int* slots, int B, int width, int max_q_len, cudaStream_t stream) {
     if (B == 0) return 0;
     MYNAH_REQUIRE(B > 0 && B <= 65535 && width > 0, "rglru_scan: bad sizes B=%d width=%d", B, width);
+    if (max_q_len >= SCAN_LONG) {                                    // some sequence is long: the kernel that cuts those into pieces
+        const dim3 pgrid(ceil_div(width, 32), B), pblock(32, SCAN_PIECES);
+        if (dtype == MYNAH_F32)
+            mynah_launch(rglru_scan_pieces_kernel<float>, pgrid, pblock, 0, stream, a, bx, (const float*)y, state, n_slots, (float*)out, cu_q, slots, width);
+        else if (dtype == MYNAH_BF16)
+            mynah_launch(rglru_scan_pieces_kernel<bf16>, pgrid, pblock, 0, stream, a, bx, (const bf16*)y, state, n_slots, (bf16*)out, cu_q, slots, width);
+        else
+            return mynah_fail("rglru_scan: unsupported dtype %d", dtype);
+        return mynah_check_launch("rglru_scan_pieces");
+    }
     const int threads = width >= 4096 ? 128 : 64;
     const dim3 grid(ceil_div(width, threads), B);
     if (dtype == MYNAH_F32)

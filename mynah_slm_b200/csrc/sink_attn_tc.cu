@@ -6,7 +6,7 @@
 //                   maximum and sum over the visible keys, 64 queries of one head a CTA (mma.sync m16n8k16).
 //   sink_mix_tc     a CTA takes 16 consecutive queries of a sequence, ALL score heads, up to 16 output heads, and a
 //                   share of the key tiles (32 keys a tile). Per tile: for every kv head, its K tile and the queries
-//                   of its heads stream through shared memory (two stages); the warps form the scores and write
+//                   of its heads stream through shared memory (several stages in flight); the warps form the scores and write
 //                   w_g = exp2(s_g - lse_g) (fp32, zero where masked) to shared memory. Then every warp takes two
 //                   output heads: it mixes the weights of all heads (fp32, m_h = sum_g talk[h, g] w_g) straight into
 //                   the A fragments of the product with V, split in two bfloat16 terms (m = hi + lo, so that the
@@ -26,6 +26,7 @@ constexpr int MROWS = 16;             // queries per CTA of the mix kernel
 constexpr int MKEYS = 32;             // its key tile
 constexpr int MWARPS = 8;
 constexpr int MHO = 2 * MWARPS;       // output heads per CTA
+constexpr int MSTAGES_MAX = 8;        // stages of (K tile, queries) in flight, at most
 constexpr int PS_LD = MKEYS + 8;      // row stride of the weights in shared memory (floats)
 static_assert(PAGE_TOKENS % MKEYS == 0, "a key tile lies inside a page");
 
@@ -36,6 +37,18 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool 
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+// waits until at most n of the newest groups are in flight (n below MSTAGES_MAX)
+__device__ __forceinline__ void cp_async_wait_upto(int n) {
+    switch (n) {
+        case 0: cp_async_wait<0>(); break;
+        case 1: cp_async_wait<1>(); break;
+        case 2: cp_async_wait<2>(); break;
+        case 3: cp_async_wait<3>(); break;
+        case 4: cp_async_wait<4>(); break;
+        case 5: cp_async_wait<5>(); break;
+        default: cp_async_wait<6>(); break;
+    }
+}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -63,7 +76,7 @@ __device__ __forceinline__ void split_bf16(float m0, float m1, uint32_t& hi, uin
 template <int CH> __device__ __forceinline__ int swz(int r, int c) { return (r * CH + (c ^ (r & 7))) * 16; }
 
 struct SinkTcArgs {
-    int B, H, G, T, window, splits, interleaved, n_pos_v;
+    int B, H, G, T, window, splits, interleaved, n_pos_v, stages;
     float scale_log2;                 // the score's scale times log2(e)
 };
 
@@ -193,12 +206,19 @@ sink_lse_tc_kernel(const bf16* __restrict__ q, float* __restrict__ lse2, const b
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// Shared memory of the mix kernel: V tiles of all kv heads, the weights of all heads, two stages of (K tile of one kv
-// head, queries of its heads), this CTA's rows of talk, the queries' lse2.
+// Shared memory of the mix kernel: V tiles of all kv heads, the weights of all heads, `stages` stages of (K tile of one
+// kv head, queries of its heads), this CTA's rows of talk, the queries' lse2. A step's compute is short beside the
+// latency of its loads, so as many stages are in flight as fit (at most as many as kv heads, two at least: a tile's
+// V travels with the stage that is asked for at the tile's first step and must have landed by its last).
 __host__ __device__ inline size_t mix_stage_bytes(int rep, int HD) { return (size_t)(MKEYS + rep * MROWS) * HD * 2; }
-__host__ __device__ inline size_t mix_smem_bytes(int H, int G, int HD, int VD) {
-    return (size_t)G * MKEYS * VD * 2 + (size_t)H * MROWS * PS_LD * 4 + 2 * mix_stage_bytes(H / G, HD) + (size_t)MHO * H * 4 +
+__host__ __device__ inline size_t mix_smem_bytes(int H, int G, int HD, int VD, int stages) {
+    return (size_t)G * MKEYS * VD * 2 + (size_t)H * MROWS * PS_LD * 4 + stages * mix_stage_bytes(H / G, HD) + (size_t)MHO * H * 4 +
            (size_t)H * MROWS * 4;
+}
+inline int mix_stages(int H, int G, int HD, int VD) {
+    int st = 2;
+    while (st < MSTAGES_MAX && st < G && mix_smem_bytes(H, G, HD, VD, st + 1) <= 227 * 1024) st++;
+    return st;
 }
 
 template <int HD, int VD>
@@ -214,8 +234,9 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
     const size_t stage_bytes = mix_stage_bytes(rep, HD);
     unsigned char* v_s = smem;                                                        // [G][MKEYS][VD]
     float* p_s = reinterpret_cast<float*>(v_s + (size_t)G * MKEYS * VD * 2);          // [H][MROWS][PS_LD]
-    unsigned char* st_s = reinterpret_cast<unsigned char*>(p_s + (size_t)H * MROWS * PS_LD);   // 2 x (K [MKEYS][HD], Q [rep][MROWS][HD])
-    float* talk_s = reinterpret_cast<float*>(st_s + 2 * stage_bytes);                 // [MHO][H]
+    unsigned char* st_s = reinterpret_cast<unsigned char*>(p_s + (size_t)H * MROWS * PS_LD);   // stages x (K [MKEYS][HD], Q [rep][MROWS][HD])
+    const int NST = a.stages;
+    float* talk_s = reinterpret_cast<float*>(st_s + NST * stage_bytes);               // [MHO][H]
     float* lse_s = talk_s + MHO * H;                                                  // [H][MROWS]
     griddep_wait();
     int b, tile;
@@ -246,7 +267,7 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
     // K tile of kv head c and the queries of its heads, for step s = (tile, c)
     auto load_stage = [&](int s) {
         const int kt = kt0 + s / G, c = s % G;
-        const uint32_t kb = smem_u32(st_s + (s & 1) * stage_bytes), qb = kb + MKEYS * HD * 2;
+        const uint32_t kb = smem_u32(st_s + (s % NST) * stage_bytes), qb = kb + MKEYS * HD * 2;
         const int key0 = kt * MKEYS;
         const int page = page_of(pt, b, key0);
         if (page < 0) bad = true;
@@ -260,7 +281,6 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
             const int r = i / CH, ch = i % CH, row = r % MROWS, hh = c * rep + r / MROWS;
             cp_async_16(qb + swz<CH>(r, ch), q + (size_t)(q0 + tile0 + (row < nq ? row : 0)) * ldq + (size_t)hh * HD + ch * 8, row < nq);
         }
-        cp_async_commit();
     };
     auto load_values = [&](int kt) {
         const int key0 = kt * MKEYS;
@@ -272,7 +292,6 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
             const size_t base = (((size_t)(page < 0 ? 0 : page) * G + c) * PAGE_TOKENS + key0 % PAGE_TOKENS + kr) * VD;
             cp_async_16(vb + swz<CHV>(r, ch), v_cache + base + ch * 8, kr < rows);
         }
-        cp_async_commit();
     };
 
     float o[2][NT_O][4];
@@ -282,28 +301,21 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
         for (int i = 0; i < NT_O; i++) o[hh][i][0] = o[hh][i][1] = o[hh][i][2] = o[hh][i][3] = 0.f;
     const int pos_a = p_first + g, pos_b = p_first + g + 8;
     const int n_steps = n_my * G;
-    if (n_steps > 0) load_stage(0);
+    // one group of copies a step: step s asks for stage s + NST - 1 (and, at a tile's first step, for the tile's V)
+    for (int i = 0; i < NST - 1; i++) {
+        if (i < n_steps) load_stage(i);
+        cp_async_commit();
+    }
 
     for (int s = 0; s < n_steps; s++) {
         const int kt = kt0 + s / G, c = s % G;
-        const bool more = s + 1 < n_steps;
-        if (c == 0) {
-            load_values(kt);                                     // the last tile's product with V has been left behind
-            if (more) {
-                load_stage(s + 1);
-                cp_async_wait<2>();
-            } else {
-                cp_async_wait<0>();
-            }
-        } else if (more) {
-            load_stage(s + 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        cp_async_wait_upto(NST - 2);                             // stage s has landed
+        __syncthreads();                                         // and everyone has left step s - 1: its stage, the weights
+        if (c == 0) load_values(kt);                             // and (behind a tile) the V tiles may be written again
+        if (s + NST - 1 < n_steps) load_stage(s + NST - 1);
+        cp_async_commit();
         // ---- weights of the heads of kv head c: a warp takes a head and 8 keys at a time
-        const uint32_t kb = smem_u32(st_s + (s & 1) * stage_bytes), qb = kb + MKEYS * HD * 2;
+        const uint32_t kb = smem_u32(st_s + (s % NST) * stage_bytes), qb = kb + MKEYS * HD * 2;
         const int key0 = kt * MKEYS;
         for (int idx = warp; idx < rep * (MKEYS / 8); idx += MWARPS) {
             const int r = idx / (MKEYS / 8), nt = idx % (MKEYS / 8);
@@ -330,14 +342,8 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
             *reinterpret_cast<float2*>(pr + g * PS_LD) = make_float2(w[0], w[1]);
             *reinterpret_cast<float2*>(pr + (g + 8) * PS_LD) = make_float2(w[2], w[3]);
         }
-        if (c + 1 < G) {
-            __syncthreads();                                     // the stage may be loaded again
-            continue;
-        }
-        if (G == 1) {                                            // the values were asked for in this very step
-            if (more) cp_async_wait<1>();
-            else cp_async_wait<0>();
-        }
+        if (c + 1 < G) continue;
+        if (NST > G) cp_async_wait<0>();                         // V came with a stage that nobody has waited for yet
         __syncthreads();                                         // every head's weights and the V tiles are in place
         // ---- this warp's two output heads: mix, split, multiply with V
         const int h0 = hb + 2 * warp;
@@ -393,8 +399,8 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
                 }
             }
         }
-        __syncthreads();                                         // weights, V tiles and the stage may be written again
     }
+    cp_async_wait<0>();
     if (bad && tid == 0) atomicOr(status, MYNAH_ST_PAGE_RANGE);
 
     // ---- store: turned back by the query's position (one share of keys), or the raw partial sums
@@ -449,7 +455,7 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
 
 // ---------------------------------------------------------------------------------------------------------------
 // out[row] = R(-pos) sum_s part[s, row]: the shares in their order, then every pair turned back
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(64)
 sink_finish_kernel(const float* __restrict__ part, bf16* __restrict__ out, const float* __restrict__ cos_v,
                    const float* __restrict__ sin_v, const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                    int T, int H, int VD, int splits, int interleaved, int n_pos_v, int* __restrict__ status) {
@@ -463,8 +469,8 @@ sink_finish_kernel(const float* __restrict__ part, bf16* __restrict__ out, const
     }
     const int hv = VD / 2;
     const size_t ld = (size_t)H * VD;
-    for (int i = threadIdx.x; i < H * hv; i += blockDim.x) {
-        const int h = i / hv, e = i % hv;
+    for (int e = threadIdx.x; e < hv; e += blockDim.x) {
+        const int h = blockIdx.y;
         const int i0 = h * VD + (interleaved ? 2 * e : e), i1 = h * VD + (interleaved ? 2 * e + 1 : e + hv);
         float u = 0.f, v = 0.f;
         for (int s = 0; s < splits; s++) {
@@ -492,7 +498,7 @@ template <int HD, int VD>
 int launch_mix(const dim3& grid, cudaStream_t stream, const bf16* q, bf16* out, float* part, const bf16* k, const bf16* v,
                const float* lse2, const VecRef& talk, const float* cos_v, const float* sin_v, const int* cu_q,
                const int* kv_len, const PageTable& pt, const SinkTcArgs& a, int* status) {
-    const size_t smem = mix_smem_bytes(a.H, a.G, HD, VD);
+    const size_t smem = mix_smem_bytes(a.H, a.G, HD, VD, a.stages);
     if (cudaFuncSetAttribute(sink_mix_tc_kernel<HD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return mynah_fail("sink_attn_tc: %zu bytes of shared memory are not to be had", smem);
     mynah_launch(sink_mix_tc_kernel<HD, VD>, grid, dim3(MWARPS * 32), smem, stream, q, out, part, k, v, lse2, talk, cos_v, sin_v,
@@ -505,7 +511,7 @@ int launch_mix(const dim3& grid, cudaStream_t stream, const bf16* q, bf16* out, 
 // Whether the tensor-core kernels take these sizes (bfloat16 only; the general kernel of sink_attn.cu takes the rest).
 MYNAH_API int mynah_sink_attn_tc_supported(int H, int G, int dim, int vd) {
     if (!((dim == 64 || dim == 128) && (vd == 64 || vd == 128) && G > 0 && H > 0 && H % G == 0)) return 0;
-    return mix_smem_bytes(H, G, dim, vd) <= 227 * 1024 ? 1 : 0;
+    return mix_smem_bytes(H, G, dim, vd, 2) <= 227 * 1024 ? 1 : 0;
 }
 
 // q [T, H*dim] (rotated), out [T, H*vd] bfloat16; lse2 fp32 [T, H] and part fp32 [splits, T, H*vd] are scratch (part
@@ -521,7 +527,7 @@ MYNAH_API int mynah_sink_attn_tc(const void* q, void* out, float* lse2, float* p
     MYNAH_REQUIRE(mynah_sink_attn_tc_supported(H, G, dim, vd), "sink_attn_tc: H=%d G=%d dim=%d vd=%d is not taken by this kernel", H, G, dim, vd);
     MYNAH_REQUIRE(T > 0 && B > 0 && window >= 0 && splits >= 1 && splits <= 65535 && H <= 65535, "sink_attn_tc: bad sizes");
     MYNAH_REQUIRE(splits == 1 || part != nullptr, "sink_attn_tc: shares of keys need their scratch");
-    const SinkTcArgs a{B, H, G, T, window, splits, interleaved, n_pos_v, scale * 1.4426950408889634f};
+    const SinkTcArgs a{B, H, G, T, window, splits, interleaved, n_pos_v, mix_stages(H, G, dim, vd), scale * 1.4426950408889634f};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     const VecRef tk{talk, g_dtype}, sk{sink, g_dtype};
     const bf16 *qq = (const bf16*)q, *kk = (const bf16*)k_cache, *vv = (const bf16*)v_cache;
@@ -538,7 +544,7 @@ MYNAH_API int mynah_sink_attn_tc(const void* q, void* out, float* lse2, float* p
     else SINK_MIX(64, 64);
 #undef SINK_MIX
     if (rc || splits == 1) return rc;
-    mynah_launch(sink_finish_kernel, dim3(T), dim3(256), 0, stream, (const float*)part, (bf16*)out, cos_v, sin_v, tok_seq, tok_pos,
+    mynah_launch(sink_finish_kernel, dim3(T, H), dim3(64), 0, stream, (const float*)part, (bf16*)out, cos_v, sin_v, tok_seq, tok_pos,
                  T, H, vd, splits, interleaved, n_pos_v, status);
     return mynah_check_launch("sink_finish");
 }

@@ -1099,7 +1099,7 @@ def rglru_scan(a: torch.Tensor, b: torch.Tensor, y: torch.Tensor, state: torch.T
         raise KernelError("rglru_scan: shapes differ")
     out = torch.empty((T, width), dtype=y.dtype, device=y.device)
     call("mynah_rglru_scan", ptr(a), ptr(b), ptr(y), code(y.dtype), ptr(state), state.shape[0] - 1, ptr(out), ptr(ctx.cu_q),
-         ptr(ctx.slots), ctx.B, width, stream_ptr())
+         ptr(ctx.slots), ctx.B, width, int(ctx.max_q_len), stream_ptr())
     return out
 
 

@@ -112,7 +112,7 @@ _SIGNATURES: dict[str, list] = {
     "mynah_rms_pair_mean": [P, P, P, P, c_int, c_float, c_float, P, c_int, c_int, P],
     "mynah_rglru_in": [P, c_int, c_int, c_int, c_int, P, P, c_int, P, P, c_int, c_int, P],
     "mynah_rglru_gates": [P, P, P, c_int, P, P, P, c_int, c_float, P, P, c_int, c_int, c_int, P],
-    "mynah_rglru_scan": [P, P, P, c_int, P, c_int, P, P, P, c_int, c_int, P],
+    "mynah_rglru_scan": [P, P, P, c_int, P, c_int, P, P, P, c_int, c_int, c_int, P],
     "mynah_sink_attn_prep": [P, c_int, c_int, P, P, P, P, P, c_int, P, P, c_int, P, P, P, P, P, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_sink_attn": [P, P, c_int, P, P, P, P, c_int, P, P, c_int, P, P, P, P, P, c_int,

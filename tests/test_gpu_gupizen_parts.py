@@ -251,6 +251,32 @@ def test_recurrent_unit_part(width, blocks, taps):
     assert float(cache.state["S"][0].abs().max()) == 0.0 and float(cache.state["S"][2].abs().max()) == 0.0
 
 
+def test_recurrent_unit_cuts_long_sequences_into_pieces():
+    """A sequence of 128 rows or more is scanned in 32 pieces that are joined through the linear recurrence: 301 rows
+    beside a short sequence (which goes the ordinary way), then 130 more rows onto the state that was left."""
+    from mynah_slm_b200.config.spec import PartSpec
+    from mynah_slm_b200.parts import CacheView
+    D, width, blocks, taps = 24, 40, 2, 3
+    rng = np.random.default_rng(77)
+    bw = width // blocks
+    W = {"y": rng.normal(size=(width, D)) / np.sqrt(D), "y.b": 0.3 * rng.normal(size=width), "x": rng.normal(size=(width, D)) / np.sqrt(D),
+         "x.b": 0.3 * rng.normal(size=width), "conv": 0.4 * rng.normal(size=(width, taps)), "conv.b": 0.2 * rng.normal(size=width),
+         "ra": rng.normal(size=(blocks, bw, bw)) / np.sqrt(bw), "ra.b": 0.3 * rng.normal(size=(blocks, bw)),
+         "ri": rng.normal(size=(blocks, bw, bw)) / np.sqrt(bw), "ri.b": 0.3 * rng.normal(size=(blocks, bw)),
+         "lam": -4.0 + 1.5 * rng.normal(size=width), "o": rng.normal(size=(D, width)) / np.sqrt(width)}     # slow decays: far rows count
+    names = {"y": "y", "y_bias": "y.b", "x": "x", "x_bias": "x.b", "conv_name": "conv", "conv_bias": "conv.b", "ra": "ra",
+             "ra_bias": "ra.b", "ri": "ri", "ri_bias": "ri.b", "lam": "lam", "o": "o"}
+    part = bound("mixer", PartSpec("rglru", {"hidden_size": D, "width": width, "blocks": blocks, "conv": taps, "decay_scale": 8.0, **names}), W)
+    m = {"width": width, "blocks": blocks, "conv": taps}
+    ha, hb = rng.normal(size=(431, D)), rng.normal(size=(50, D))
+    ref_a, ref_b = plain.rglru(ha, W, m), plain.rglru(hb, W, m)
+    cache = CacheView(state=_states(part.state_request(), 3))
+    out = part.forward(rows(np.concatenate([hb, ha[:301]], 0)), ctx_for([50, 301], [2, 0]), cache).cpu().numpy()
+    more = part.forward(rows(ha[301:]), ctx_for([130], [0], starts=[301]), cache).cpu().numpy()
+    assert rel(ref_b, out[:50]) < 2e-5
+    assert rel(ref_a, np.concatenate([out[50:], more], 0)) < 2e-5
+
+
 def test_recurrent_unit_keeps_what_it_is_told_to():
     """A decay parameter far below zero keeps the state for hundreds of tokens: the first token still shows at the end
     (control), and the part carries it there whole and token by token."""
