@@ -185,6 +185,21 @@ __global__ void moe_combine_kernel(const float* __restrict__ o, const int* __res
     }
 }
 
+// eight consecutive values (16-byte aligned for bfloat16, 32 for float) as fp32
+__device__ __forceinline__ void load8_f32(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8_f32(const bf16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
 // The learned router: one CTA a token; a warp an expert's logit at a time, then one thread picks.
 constexpr int ROUTER_THREADS = 128;
 template <typename TA>
@@ -203,10 +218,20 @@ moe_router_kernel(const TA* __restrict__ h, const TA* __restrict__ w, VecRef bia
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const TA* x = h + (size_t)t * D;
+    // rows of a multiple of 8 values go 8 values a lane and load (16 or 32 bytes), four experts of a warp in flight
+    const int D8 = D % 8 == 0 ? D : 0;
     for (int e = warp; e < E; e += ROUTER_THREADS / 32) {
         const TA* wr = w + (size_t)e * D;
         float acc = 0.f;
-        for (int d = lane; d < D; d += 32) acc = fmaf(to_f32(x[d]), to_f32(wr[d]), acc);
+#pragma unroll 2
+        for (int d = lane * 8; d < D8; d += 256) {
+            float xv[8], wv[8];
+            load8_f32(x + d, xv);
+            load8_f32(wr + d, wv);
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc = fmaf(xv[i], wv[i], acc);
+        }
+        for (int d = D8 + lane; d < D; d += 32) acc = fmaf(to_f32(x[d]), to_f32(wr[d]), acc);
         acc = warp_sum(acc);
         if (lane == 0) z[e] = acc + bias.at(e);
     }

@@ -66,17 +66,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&h);
 }
-// m = hi + lo in two bfloat16 terms
+// m = hi + lo in two bfloat16 terms: hi is m cut off behind bfloat16's bits (a bit pattern, no rounding), lo the exact
+// remainder rounded to bfloat16, so hi + lo keeps 16 bits of m
 __device__ __forceinline__ void split_bf16(float m0, float m1, uint32_t& hi, uint32_t& lo) {
-    const bf16 h0 = __float2bfloat16_rn(m0), h1 = __float2bfloat16_rn(m1);
-    hi = pack_bf16(__bfloat162float(h0), __bfloat162float(h1));
-    lo = pack_bf16(m0 - __bfloat162float(h0), m1 - __bfloat162float(h1));
+    const uint32_t b0 = __float_as_uint(m0), b1 = __float_as_uint(m1);
+    hi = __byte_perm(b0, b1, 0x7632);
+    lo = pack_bf16(m0 - __uint_as_float(b0 & 0xffff0000u), m1 - __uint_as_float(b1 & 0xffff0000u));
 }
 // byte offset of the 16-byte chunk c of row r in a tile whose rows hold CH chunks
 template <int CH> __device__ __forceinline__ int swz(int r, int c) { return (r * CH + (c ^ (r & 7))) * 16; }
 
 struct SinkTcArgs {
-    int B, H, G, T, window, splits, interleaved, n_pos_v, stages;
+    int B, H, G, T, window, splits, interleaved, n_pos_v, stages, cg;
     float scale_log2;                 // the score's scale times log2(e)
 };
 
@@ -210,14 +211,19 @@ sink_lse_tc_kernel(const bf16* __restrict__ q, float* __restrict__ lse2, const b
 // kv head, queries of its heads), this CTA's rows of talk, the queries' lse2. A step's compute is short beside the
 // latency of its loads, so as many stages are in flight as fit (at most as many as kv heads, two at least: a tile's
 // V travels with the stage that is asked for at the tile's first step and must have landed by its last).
-__host__ __device__ inline size_t mix_stage_bytes(int rep, int HD) { return (size_t)(MKEYS + rep * MROWS) * HD * 2; }
-__host__ __device__ inline size_t mix_smem_bytes(int H, int G, int HD, int VD, int stages) {
-    return (size_t)G * MKEYS * VD * 2 + (size_t)H * MROWS * PS_LD * 4 + stages * mix_stage_bytes(H / G, HD) + (size_t)MHO * H * 4 +
+// A stage holds `cg` kv heads (two where that leaves room for three stages: half as many steps and barriers a tile, and
+// two independent products a warp and step).
+__host__ __device__ inline size_t mix_stage_bytes(int rep, int HD, int cg) { return (size_t)cg * (MKEYS + rep * MROWS) * HD * 2; }
+__host__ __device__ inline size_t mix_smem_bytes(int H, int G, int HD, int VD, int stages, int cg) {
+    return (size_t)G * MKEYS * VD * 2 + (size_t)H * MROWS * PS_LD * 4 + stages * mix_stage_bytes(H / G, HD, cg) + (size_t)MHO * H * 4 +
            (size_t)H * MROWS * 4;
 }
-inline int mix_stages(int H, int G, int HD, int VD) {
+inline int mix_heads_a_stage(int H, int G, int HD, int VD) {
+    return G % 2 == 0 && mix_smem_bytes(H, G, HD, VD, 3, 2) <= 227 * 1024 ? 2 : 1;
+}
+inline int mix_stages(int H, int G, int HD, int VD, int cg) {
     int st = 2;
-    while (st < MSTAGES_MAX && st < G && mix_smem_bytes(H, G, HD, VD, st + 1) <= 227 * 1024) st++;
+    while (st < MSTAGES_MAX && st < G / cg && mix_smem_bytes(H, G, HD, VD, st + 1, cg) <= 227 * 1024) st++;
     return st;
 }
 
@@ -231,7 +237,8 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
     constexpr int CH = HD / 8, CHV = VD / 8, KSTEPS = HD / 16, NT_O = VD / 8;
     extern __shared__ __align__(128) unsigned char smem[];
     const int H = a.H, G = a.G, rep = H / G;
-    const size_t stage_bytes = mix_stage_bytes(rep, HD);
+    const int CG = a.cg, GS = G / CG;                     // kv heads a step, steps a tile
+    const size_t stage_bytes = mix_stage_bytes(rep, HD, CG);
     unsigned char* v_s = smem;                                                        // [G][MKEYS][VD]
     float* p_s = reinterpret_cast<float*>(v_s + (size_t)G * MKEYS * VD * 2);          // [H][MROWS][PS_LD]
     unsigned char* st_s = reinterpret_cast<unsigned char*>(p_s + (size_t)H * MROWS * PS_LD);   // stages x (K [MKEYS][HD], Q [rep][MROWS][HD])
@@ -257,28 +264,36 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
     const int n_my = max(0, min(kt_last + 1, kt0 + per) - kt0);
     const size_t ldq = (size_t)H * HD;
 
-    for (int i = tid; i < MHO * H; i += blockDim.x) talk_s[i] = hb + i / H < H ? talk.at((hb + i / H) * H + i % H) : 0.f;
-    for (int i = tid; i < H * MROWS; i += blockDim.x) {
+    for (int i = tid; i < MHO * H; i += MWARPS * 32) {           // [warp][score head][its two output heads]
+        const int ho = i / H, hg = i % H;
+        talk_s[((ho >> 1) * H + hg) * 2 + (ho & 1)] = hb + ho < H ? talk.at((hb + ho) * H + hg) : 0.f;
+    }
+    for (int i = tid; i < H * MROWS; i += MWARPS * 32) {
         const int r = i % MROWS;
         lse_s[i] = r < nq ? lse2[(size_t)(q0 + tile0 + r) * H + i / MROWS] : 0.f;
     }
 
     bool bad = false;
-    // K tile of kv head c and the queries of its heads, for step s = (tile, c)
+    // K tiles of CG kv heads and the queries of their heads, for step s = (tile, group of kv heads)
+    int looked_kt = -1, looked_page = -1;                        // a tile's page is looked up once, not once a step
     auto load_stage = [&](int s) {
-        const int kt = kt0 + s / G, c = s % G;
-        const uint32_t kb = smem_u32(st_s + (s % NST) * stage_bytes), qb = kb + MKEYS * HD * 2;
+        const int kt = kt0 + s / GS, c_first = (s % GS) * CG;
+        const uint32_t kb = smem_u32(st_s + (s % NST) * stage_bytes), qb = kb + CG * MKEYS * HD * 2;
         const int key0 = kt * MKEYS;
-        const int page = page_of(pt, b, key0);
-        if (page < 0) bad = true;
-        const size_t base = (((size_t)(page < 0 ? 0 : page) * G + c) * PAGE_TOKENS + key0 % PAGE_TOKENS) * HD;
-        const int rows = page < 0 ? 0 : min(MKEYS, n_kv - key0);
-        for (int i = tid; i < MKEYS * CH; i += blockDim.x) {
-            const int r = i / CH, ch = i % CH;
-            cp_async_16(kb + swz<CH>(r, ch), k_cache + base + (size_t)r * HD + ch * 8, r < rows);
+        if (kt != looked_kt) {
+            looked_page = page_of(pt, b, key0);
+            looked_kt = kt;
         }
-        for (int i = tid; i < rep * MROWS * CH; i += blockDim.x) {
-            const int r = i / CH, ch = i % CH, row = r % MROWS, hh = c * rep + r / MROWS;
+        const int page = looked_page;
+        if (page < 0) bad = true;
+        const int rows = page < 0 ? 0 : min(MKEYS, n_kv - key0);
+        for (int i = tid; i < CG * MKEYS * CH; i += MWARPS * 32) {
+            const int r = i / CH, ch = i % CH, j = r / MKEYS, kr = r % MKEYS;
+            const size_t base = (((size_t)(page < 0 ? 0 : page) * G + c_first + j) * PAGE_TOKENS + key0 % PAGE_TOKENS + kr) * HD;
+            cp_async_16(kb + swz<CH>(r, ch), k_cache + base + ch * 8, kr < rows);
+        }
+        for (int i = tid; i < CG * rep * MROWS * CH; i += MWARPS * 32) {
+            const int r = i / CH, ch = i % CH, row = r % MROWS, hh = c_first * rep + r / MROWS;
             cp_async_16(qb + swz<CH>(r, ch), q + (size_t)(q0 + tile0 + (row < nq ? row : 0)) * ldq + (size_t)hh * HD + ch * 8, row < nq);
         }
     };
@@ -287,7 +302,7 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
         const int page = page_of(pt, b, key0);
         const int rows = page < 0 ? 0 : min(MKEYS, n_kv - key0);
         const uint32_t vb = smem_u32(v_s);
-        for (int i = tid; i < G * MKEYS * CHV; i += blockDim.x) {
+        for (int i = tid; i < G * MKEYS * CHV; i += MWARPS * 32) {
             const int r = i / CHV, ch = i % CHV, c = r / MKEYS, kr = r % MKEYS;
             const size_t base = (((size_t)(page < 0 ? 0 : page) * G + c) * PAGE_TOKENS + key0 % PAGE_TOKENS + kr) * VD;
             cp_async_16(vb + swz<CHV>(r, ch), v_cache + base + ch * 8, kr < rows);
@@ -300,7 +315,7 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
 #pragma unroll
         for (int i = 0; i < NT_O; i++) o[hh][i][0] = o[hh][i][1] = o[hh][i][2] = o[hh][i][3] = 0.f;
     const int pos_a = p_first + g, pos_b = p_first + g + 8;
-    const int n_steps = n_my * G;
+    const int n_steps = n_my * GS;
     // one group of copies a step: step s asks for stage s + NST - 1 (and, at a tile's first step, for the tile's V)
     for (int i = 0; i < NST - 1; i++) {
         if (i < n_steps) load_stage(i);
@@ -308,28 +323,30 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
     }
 
     for (int s = 0; s < n_steps; s++) {
-        const int kt = kt0 + s / G, c = s % G;
+        const int kt = kt0 + s / GS, cgi = s % GS;
         cp_async_wait_upto(NST - 2);                             // stage s has landed
         __syncthreads();                                         // and everyone has left step s - 1: its stage, the weights
-        if (c == 0) load_values(kt);                             // and (behind a tile) the V tiles may be written again
+        if (cgi == 0) load_values(kt);                             // and (behind a tile) the V tiles may be written again
         if (s + NST - 1 < n_steps) load_stage(s + NST - 1);
         cp_async_commit();
-        // ---- weights of the heads of kv head c: a warp takes a head and 8 keys at a time
-        const uint32_t kb = smem_u32(st_s + (s % NST) * stage_bytes), qb = kb + MKEYS * HD * 2;
+        // ---- weights of the heads of these kv heads: a warp takes a head and 8 keys at a time
+        const uint32_t kb = smem_u32(st_s + (s % NST) * stage_bytes), qb = kb + CG * MKEYS * HD * 2;
         const int key0 = kt * MKEYS;
-        for (int idx = warp; idx < rep * (MKEYS / 8); idx += MWARPS) {
-            const int r = idx / (MKEYS / 8), nt = idx % (MKEYS / 8);
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int idx = warp; idx < CG * rep * (MKEYS / 8); idx += MWARPS) {
+            const int r = idx / (MKEYS / 8), nt = idx % (MKEYS / 8), j = r / rep;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};    // two chains over k, added at the end
 #pragma unroll
             for (int k2 = 0; k2 < KSTEPS / 2; k2++) {
                 uint32_t qa0[4], qa1[4], kf[4];
                 ldmatrix_x4(qa0, qb + swz<CH>(r * MROWS + (mat & 1) * 8 + rr, k2 * 4 + (mat >> 1)));
                 ldmatrix_x4(qa1, qb + swz<CH>(r * MROWS + (mat & 1) * 8 + rr, k2 * 4 + 2 + (mat >> 1)));
-                ldmatrix_x4(kf, kb + swz<CH>(nt * 8 + rr, k2 * 4 + mat));
+                ldmatrix_x4(kf, kb + swz<CH>(j * MKEYS + nt * 8 + rr, k2 * 4 + mat));
                 mma_bf16(acc, qa0, kf[0], kf[1]);
-                mma_bf16(acc, qa1, kf[2], kf[3]);
+                mma_bf16(acc1, qa1, kf[2], kf[3]);
             }
-            const int head = c * rep + r;
+#pragma unroll
+            for (int e = 0; e < 4; e++) acc[e] += acc1[e];
+            const int head = cgi * CG * rep + r;
             float w[4];
 #pragma unroll
             for (int e = 0; e < 4; e++) {
@@ -342,15 +359,14 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
             *reinterpret_cast<float2*>(pr + g * PS_LD) = make_float2(w[0], w[1]);
             *reinterpret_cast<float2*>(pr + (g + 8) * PS_LD) = make_float2(w[2], w[3]);
         }
-        if (c + 1 < G) continue;
-        if (NST > G) cp_async_wait<0>();                         // V came with a stage that nobody has waited for yet
+        if (cgi + 1 < GS) continue;
+        if (NST > GS) cp_async_wait<0>();                         // V came with a stage that nobody has waited for yet
         __syncthreads();                                         // every head's weights and the V tiles are in place
         // ---- this warp's two output heads: mix, split, multiply with V
         const int h0 = hb + 2 * warp;
         if (h0 < H) {
             const bool two = h0 + 1 < H;
-            const float* tk0 = talk_s + (2 * warp) * H;
-            const float* tk1 = tk0 + H;
+            const float2* tk = reinterpret_cast<const float2*>(talk_s) + warp * H;
             const uint32_t vb = smem_u32(v_s);
             const int c0 = h0 / rep, c1 = two ? (h0 + 1) / rep : c0;
 #pragma unroll
@@ -359,13 +375,15 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
 #pragma unroll
                 for (int e = 0; e < 8; e++) m0[e] = m1[e] = 0.f;
                 const float* pr = p_s + ks * 16 + t * 2;
+#pragma unroll 4
                 for (int hg = 0; hg < H; hg++) {
                     const float* ph = pr + (size_t)hg * MROWS * PS_LD;
                     const float2 x0 = *reinterpret_cast<const float2*>(ph + g * PS_LD);
                     const float2 x1 = *reinterpret_cast<const float2*>(ph + (g + 8) * PS_LD);
                     const float2 x2 = *reinterpret_cast<const float2*>(ph + g * PS_LD + 8);
                     const float2 x3 = *reinterpret_cast<const float2*>(ph + (g + 8) * PS_LD + 8);
-                    const float t0 = tk0[hg], t1 = tk1[hg];
+                    const float2 tt = tk[hg];
+                    const float t0 = tt.x, t1 = tt.y;
                     m0[0] = fmaf(t0, x0.x, m0[0]); m0[1] = fmaf(t0, x0.y, m0[1]);
                     m0[2] = fmaf(t0, x1.x, m0[2]); m0[3] = fmaf(t0, x1.y, m0[3]);
                     m0[4] = fmaf(t0, x2.x, m0[4]); m0[5] = fmaf(t0, x2.y, m0[5]);
@@ -498,7 +516,7 @@ template <int HD, int VD>
 int launch_mix(const dim3& grid, cudaStream_t stream, const bf16* q, bf16* out, float* part, const bf16* k, const bf16* v,
                const float* lse2, const VecRef& talk, const float* cos_v, const float* sin_v, const int* cu_q,
                const int* kv_len, const PageTable& pt, const SinkTcArgs& a, int* status) {
-    const size_t smem = mix_smem_bytes(a.H, a.G, HD, VD, a.stages);
+    const size_t smem = mix_smem_bytes(a.H, a.G, HD, VD, a.stages, a.cg);
     if (cudaFuncSetAttribute(sink_mix_tc_kernel<HD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return mynah_fail("sink_attn_tc: %zu bytes of shared memory are not to be had", smem);
     mynah_launch(sink_mix_tc_kernel<HD, VD>, grid, dim3(MWARPS * 32), smem, stream, q, out, part, k, v, lse2, talk, cos_v, sin_v,
@@ -511,7 +529,7 @@ int launch_mix(const dim3& grid, cudaStream_t stream, const bf16* q, bf16* out, 
 // Whether the tensor-core kernels take these sizes (bfloat16 only; the general kernel of sink_attn.cu takes the rest).
 MYNAH_API int mynah_sink_attn_tc_supported(int H, int G, int dim, int vd) {
     if (!((dim == 64 || dim == 128) && (vd == 64 || vd == 128) && G > 0 && H > 0 && H % G == 0)) return 0;
-    return mix_smem_bytes(H, G, dim, vd, 2) <= 227 * 1024 ? 1 : 0;
+    return mix_smem_bytes(H, G, dim, vd, 2, 1) <= 227 * 1024 ? 1 : 0;
 }
 
 // q [T, H*dim] (rotated), out [T, H*vd] bfloat16; lse2 fp32 [T, H] and part fp32 [splits, T, H*vd] are scratch (part
@@ -527,7 +545,8 @@ MYNAH_API int mynah_sink_attn_tc(const void* q, void* out, float* lse2, float* p
     MYNAH_REQUIRE(mynah_sink_attn_tc_supported(H, G, dim, vd), "sink_attn_tc: H=%d G=%d dim=%d vd=%d is not taken by this kernel", H, G, dim, vd);
     MYNAH_REQUIRE(T > 0 && B > 0 && window >= 0 && splits >= 1 && splits <= 65535 && H <= 65535, "sink_attn_tc: bad sizes");
     MYNAH_REQUIRE(splits == 1 || part != nullptr, "sink_attn_tc: shares of keys need their scratch");
-    const SinkTcArgs a{B, H, G, T, window, splits, interleaved, n_pos_v, mix_stages(H, G, dim, vd), scale * 1.4426950408889634f};
+    const int cg = mix_heads_a_stage(H, G, dim, vd);
+    const SinkTcArgs a{B, H, G, T, window, splits, interleaved, n_pos_v, mix_stages(H, G, dim, vd, cg), cg, scale * 1.4426950408889634f};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     const VecRef tk{talk, g_dtype}, sk{sink, g_dtype};
     const bf16 *qq = (const bf16*)q, *kk = (const bf16*)k_cache, *vv = (const bf16*)v_cache;
