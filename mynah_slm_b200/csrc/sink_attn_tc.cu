@@ -2,8 +2,9 @@
 // cache, head sizes 64 and 128. The weights of a key are mixed over all heads, so no head can be computed alone. Since
 // the mixing is linear, the softmax is first finished per head and the rest is one pass over the keys:
 //
-//   sink_lse_tc     per query and head, log2 of the denominator (sink included) of the scaled scores: an online
-//                   maximum and sum over the visible keys, 64 queries of one head a CTA (mma.sync m16n8k16).
+//   sink_lse_tc     per query and head, the maximum and the sum of the denominator of the scaled scores: online over
+//                   the visible keys, 64 queries of one head a CTA (mma.sync m16n8k16), a decode step's pages in
+//                   shares; the mix kernel folds the shares and the sink into log2 of the denominator.
 //   sink_mix_tc     a CTA takes 16 consecutive queries of a sequence, ALL score heads, up to 16 output heads, and a
 //                   share of the key tiles (32 keys a tile). Per tile: for every kv head, its K tile and the queries
 //                   of its heads stream through shared memory (several stages in flight); the warps form the scores and write
@@ -82,10 +83,11 @@ struct SinkTcArgs {
 };
 
 // ---------------------------------------------------------------------------------------------------------------
-// log2 of each head's denominator: lse2[row, h] = log2(2^(sink_h log2 e) + sum_j 2^(scale_log2 q.k_j))
+// Each head's maximum m and sum_j 2^(scale_log2 q.k_j - m) over one share (blockIdx.z) of the pages a query tile sees:
+// stats[share, row, h] = (m, sum). The mix kernel folds the shares in their order and adds the sink.
 template <int HD>
 __global__ void __launch_bounds__(128)
-sink_lse_tc_kernel(const bf16* __restrict__ q, float* __restrict__ lse2, const bf16* __restrict__ k_cache, VecRef sink,
+sink_lse_tc_kernel(const bf16* __restrict__ q, float2* __restrict__ stats, const bf16* __restrict__ k_cache,
                    const int* __restrict__ cu_q, const int* __restrict__ kv_len, PageTable pt, SinkTcArgs a,
                    int* __restrict__ status) {
     constexpr int CH = HD / 8, KSTEPS = HD / 16, NT_S = LKT / 8;
@@ -107,8 +109,15 @@ sink_lse_tc_kernel(const bf16* __restrict__ q, float* __restrict__ lse2, const b
     const int g = lane >> 2, t = lane & 3;
     const int p_first = past + tile0, p_last = p_first + nq - 1;
     const int k_lo = a.window > 0 ? max(0, p_first - a.window + 1) : 0;
-    const int pg_first = k_lo / LKT, pg_last = p_last / LKT;
+    const int pg_lo = k_lo / LKT, pg_hi = p_last / LKT;
+    const int pg_per = (pg_hi - pg_lo + 1 + a.splits - 1) / a.splits;
+    const int pg_first = pg_lo + (int)blockIdx.z * pg_per, pg_last = min(pg_hi, pg_first + pg_per - 1);
     const size_t ldq = (size_t)a.H * HD;
+    float2* st = stats + ((size_t)blockIdx.z * a.T + q0 + tile0) * a.H + h;
+    if (pg_first > pg_last) {                                    // a share without pages
+        for (int r = tid; r < nq; r += blockDim.x) st[(size_t)r * a.H] = make_float2(-INFINITY, 0.f);
+        return;
+    }
 
     const uint32_t q_base = smem_u32(q_s);
     for (int i = tid; i < LQT * CH; i += blockDim.x) {
@@ -192,7 +201,6 @@ sink_lse_tc_kernel(const bf16* __restrict__ q, float* __restrict__ lse2, const b
         __syncthreads();
     }
     if (bad && tid == 0) atomicOr(status, MYNAH_ST_PAGE_RANGE);
-    const float sk2 = sink.at(h) * 1.4426950408889634f;
 #pragma unroll
     for (int j = 0; j < 2; j++) {
         float l = l_run[j];
@@ -200,9 +208,7 @@ sink_lse_tc_kernel(const bf16* __restrict__ q, float* __restrict__ lse2, const b
         l += __shfl_xor_sync(0xffffffffu, l, 2);
         const int r = warp * 16 + g + 8 * j;
         if (r >= nq || t != 0) continue;
-        const float m2 = fmaxf(m_run[j], sk2);
-        const float tot = (l > 0.f ? l * exp2f(m_run[j] - m2) : 0.f) + exp2f(sk2 - m2);
-        lse2[(size_t)(q0 + tile0 + r) * a.H + h] = m2 + log2f(tot);
+        st[(size_t)r * a.H] = make_float2(m_run[j], l);
     }
 }
 
@@ -230,8 +236,8 @@ inline int mix_stages(int H, int G, int HD, int VD, int cg) {
 template <int HD, int VD>
 __global__ void __launch_bounds__(MWARPS * 32, 1)
 sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __restrict__ part,
-                   const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, const float* __restrict__ lse2,
-                   VecRef talk, const float* __restrict__ cos_v, const float* __restrict__ sin_v,
+                   const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache, const float2* __restrict__ stats,
+                   VecRef talk, VecRef sink, const float* __restrict__ cos_v, const float* __restrict__ sin_v,
                    const int* __restrict__ cu_q, const int* __restrict__ kv_len, PageTable pt, SinkTcArgs a,
                    int* __restrict__ status) {
     constexpr int CH = HD / 8, CHV = VD / 8, KSTEPS = HD / 16, NT_O = VD / 8;
@@ -268,9 +274,23 @@ sink_mix_tc_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, float* __
         const int ho = i / H, hg = i % H;
         talk_s[((ho >> 1) * H + hg) * 2 + (ho & 1)] = hb + ho < H ? talk.at((hb + ho) * H + hg) : 0.f;
     }
+    // log2 of each head's denominator: the shares' (maximum, sum) folded in their order, then the sink
     for (int i = tid; i < H * MROWS; i += MWARPS * 32) {
-        const int r = i % MROWS;
-        lse_s[i] = r < nq ? lse2[(size_t)(q0 + tile0 + r) * H + i / MROWS] : 0.f;
+        const int r = i % MROWS, hh = i / MROWS;
+        float lse = 0.f;
+        if (r < nq) {
+            const float2* st = stats + (size_t)(q0 + tile0 + r) * H + hh;
+            const float sk2 = sink.at(hh) * 1.4426950408889634f;
+            float m = sk2;
+            for (int z = 0; z < a.splits; z++) m = fmaxf(m, st[(size_t)z * a.T * H].x);
+            float tot = 0.f;
+            for (int z = 0; z < a.splits; z++) {
+                const float2 v = st[(size_t)z * a.T * H];
+                if (v.y > 0.f) tot += v.y * exp2f(v.x - m);
+            }
+            lse = m + log2f(tot + exp2f(sk2 - m));
+        }
+        lse_s[i] = lse;
     }
 
     bool bad = false;
@@ -503,23 +523,23 @@ sink_finish_kernel(const float* __restrict__ part, bf16* __restrict__ out, const
 }
 
 template <int HD>
-int launch_lse(const dim3& grid, cudaStream_t stream, const bf16* q, float* lse2, const bf16* k, const VecRef& sink,
+int launch_lse(const dim3& grid, cudaStream_t stream, const bf16* q, float2* stats, const bf16* k,
                const int* cu_q, const int* kv_len, const PageTable& pt, const SinkTcArgs& a, int* status) {
     const size_t smem = (size_t)LQT * HD * 2 + 2 * (size_t)LKT * HD * 2;
     if (cudaFuncSetAttribute(sink_lse_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return mynah_fail("sink_attn_tc: %zu bytes of shared memory are not to be had", smem);
-    mynah_launch(sink_lse_tc_kernel<HD>, grid, dim3(128), smem, stream, q, lse2, k, sink, cu_q, kv_len, pt, a, status);
+    mynah_launch(sink_lse_tc_kernel<HD>, grid, dim3(128), smem, stream, q, stats, k, cu_q, kv_len, pt, a, status);
     return mynah_check_launch("sink_lse_tc");
 }
 
 template <int HD, int VD>
 int launch_mix(const dim3& grid, cudaStream_t stream, const bf16* q, bf16* out, float* part, const bf16* k, const bf16* v,
-               const float* lse2, const VecRef& talk, const float* cos_v, const float* sin_v, const int* cu_q,
+               const float2* stats, const VecRef& talk, const VecRef& sink, const float* cos_v, const float* sin_v, const int* cu_q,
                const int* kv_len, const PageTable& pt, const SinkTcArgs& a, int* status) {
     const size_t smem = mix_smem_bytes(a.H, a.G, HD, VD, a.stages, a.cg);
     if (cudaFuncSetAttribute(sink_mix_tc_kernel<HD, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return mynah_fail("sink_attn_tc: %zu bytes of shared memory are not to be had", smem);
-    mynah_launch(sink_mix_tc_kernel<HD, VD>, grid, dim3(MWARPS * 32), smem, stream, q, out, part, k, v, lse2, talk, cos_v, sin_v,
+    mynah_launch(sink_mix_tc_kernel<HD, VD>, grid, dim3(MWARPS * 32), smem, stream, q, out, part, k, v, stats, talk, sink, cos_v, sin_v,
                  cu_q, kv_len, pt, a, status);
     return mynah_check_launch("sink_mix_tc");
 }
@@ -532,8 +552,8 @@ MYNAH_API int mynah_sink_attn_tc_supported(int H, int G, int dim, int vd) {
     return mix_smem_bytes(H, G, dim, vd, 2, 1) <= 227 * 1024 ? 1 : 0;
 }
 
-// q [T, H*dim] (rotated), out [T, H*vd] bfloat16; lse2 fp32 [T, H] and part fp32 [splits, T, H*vd] are scratch (part
-// may be null with one share of keys); talk [H, H], sink [H] in g_dtype. B sequences with rows cu_q[b]..cu_q[b+1] that
+// q [T, H*dim] (rotated), out [T, H*vd] bfloat16; lse2 fp32 [splits, T, H, 2] (8-byte aligned) and part fp32
+// [splits, T, H*vd] are scratch (part may be null with one share of keys); talk [H, H], sink [H] in g_dtype. B sequences with rows cu_q[b]..cu_q[b+1] that
 // end at position kv_len[b] - 1.
 MYNAH_API int mynah_sink_attn_tc(const void* q, void* out, float* lse2, float* part, const void* k_cache, const void* v_cache,
                                  const void* talk, const void* sink, int g_dtype, const float* cos_v, const float* sin_v,
@@ -550,13 +570,15 @@ MYNAH_API int mynah_sink_attn_tc(const void* q, void* out, float* lse2, float* p
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     const VecRef tk{talk, g_dtype}, sk{sink, g_dtype};
     const bf16 *qq = (const bf16*)q, *kk = (const bf16*)k_cache, *vv = (const bf16*)v_cache;
-    const dim3 lgrid(ceil_div(T, LQT) + B, H, 1);
-    int rc = dim == 128 ? launch_lse<128>(lgrid, stream, qq, lse2, kk, sk, cu_q, kv_len, pt, a, status)
-                        : launch_lse<64>(lgrid, stream, qq, lse2, kk, sk, cu_q, kv_len, pt, a, status);
+    MYNAH_REQUIRE((reinterpret_cast<uintptr_t>(lse2) & 7) == 0, "sink_attn_tc: scratch is not 8-byte aligned");
+    float2* stats = reinterpret_cast<float2*>(lse2);
+    const dim3 lgrid(ceil_div(T, LQT) + B, H, splits);
+    int rc = dim == 128 ? launch_lse<128>(lgrid, stream, qq, stats, kk, cu_q, kv_len, pt, a, status)
+                        : launch_lse<64>(lgrid, stream, qq, stats, kk, cu_q, kv_len, pt, a, status);
     if (rc) return rc;
     const dim3 mgrid(ceil_div(T, MROWS) + B, splits, ceil_div(H, MHO));
 #define SINK_MIX(HD_, VD_)                                                                                              \
-    rc = launch_mix<HD_, VD_>(mgrid, stream, qq, (bf16*)out, part, kk, vv, lse2, tk, cos_v, sin_v, cu_q, kv_len, pt, a, status)
+    rc = launch_mix<HD_, VD_>(mgrid, stream, qq, (bf16*)out, part, kk, vv, stats, tk, sk, cos_v, sin_v, cu_q, kv_len, pt, a, status)
     if (dim == 128 && vd == 128) SINK_MIX(128, 128);
     else if (dim == 128) SINK_MIX(128, 64);
     else if (vd == 128) SINK_MIX(64, 128);

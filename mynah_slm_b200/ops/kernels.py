@@ -1148,8 +1148,9 @@ def sink_attn_tc_supported(dtype: torch.dtype, H: int, G: int, dim: int, vd: int
 
 
 def sink_attn_tc_scratch(T: int, H: int, vd: int, splits: int) -> int:
-    """fp32 words of scratch: log2 of the denominators [T, H], and the shares' partial sums when there are several."""
-    return T * H + (splits * T * H * vd if splits > 1 else 0)
+    """fp32 words of scratch: every share's (maximum, sum) of the denominators [splits, T, H, 2], and the shares' partial
+    sums when there are several."""
+    return 2 * splits * T * H + (splits * T * H * vd if splits > 1 else 0)
 
 
 def sink_attn_tc(q: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -1171,7 +1172,7 @@ def sink_attn_tc(q: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, k_ca
         raise KernelError("sink_attn_tc: the cache pages do not have the head sizes")
     if scratch.numel() < sink_attn_tc_scratch(T, H, vd, splits):
         raise KernelError("sink_attn_tc: scratch too small")
-    part = scratch[T * H:] if splits > 1 else None
+    part = scratch[2 * splits * T * H:] if splits > 1 else None
     call("mynah_sink_attn_tc", ptr(q), ptr(out), ptr(scratch), ptr(part), ptr(k_cache), ptr(v_cache), ptr(talk), ptr(sink),
          code(talk.dtype), ptr(cos_v), ptr(sin_v), cos_v.shape[0], ptr(ctx.cu_q), ptr(ctx.kv_len), ptr(ctx.tok_seq),
          ptr(ctx.tok_pos), ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, T, ctx.B, H, G, dim, vd,
