@@ -214,6 +214,60 @@ def test_sink_attention_on_tensor_cores(monkeypatch, H, G, dim, vd, window, spli
     assert rel(plain.sink_talk_attention(hB.to(torch.float64).numpy(), W, mm, np.arange(len(hB))), tcB) < 3e-2
 
 
+@pytest.mark.parametrize("window,star", [(70, 60), (64, 64), (33, 127), (200, 3)])
+def test_tensor_core_attention_sees_a_key_up_to_the_window_edge_and_not_beyond(window, star):
+    """One key stands out (its score is 40 above the others'): every query that sees it returns that key's value,
+    mixed over the heads; the query one position beyond the window does not. In a prompt, and with single queries
+    whose keys are cut in shares, at page borders; the general kernel on the same rows says the same."""
+    from mynah_slm_b200.ops import kernels
+    H, G, dim, vd, T = 4, 2, 64, 64, 330
+    rng = np.random.default_rng(window)
+    bf = lambda a: torch.tensor(a, dtype=torch.float32).to(torch.bfloat16).to(DEV).contiguous()
+    q = np.zeros((T, H, dim))
+    q[:, :, 5] = 8.0
+    k = 0.05 * rng.normal(size=(T, G, dim))
+    k[star, :, 5] = 5.0                                             # 8 * 5 * scale(1.0) = 40
+    v = rng.normal(size=(T, G, vd))
+    talk = 0.5 * np.eye(H) + 0.3 * rng.normal(size=(H, H))
+    talk = torch.tensor(talk).to(torch.bfloat16).to(torch.float64).numpy()
+    n_pages = (T + 63) // 64
+    pages = list(rng.permutation(n_pages))
+    kc = torch.zeros((n_pages, G, 64, dim), dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros((n_pages, G, 64, vd), dtype=torch.bfloat16, device=DEV)
+    for t in range(T):
+        kc[pages[t // 64], :, t % 64] = bf(k[t])
+        vc[pages[t // 64], :, t % 64] = bf(v[t])
+    v_star = vc[pages[star // 64], :, star % 64].float().cpu().numpy()                  # [G, vd]
+    want = np.stack([talk[h].sum() * v_star[h // (H // G)] for h in range(H)]).reshape(-1)
+    cos_v = torch.ones((T, vd // 2), device=DEV)
+    sin_v = torch.zeros((T, vd // 2), device=DEV)
+    tk, sk = bf(talk), bf(np.full((H,), -30.0))
+    last_in, first_out = min(star + window - 1, T - 1), star + window
+
+    def both(ctx, rows_q, splits):
+        outs = []
+        for tc in (True, False):
+            out = torch.zeros((rows_q.shape[0], H * vd), dtype=torch.bfloat16, device=DEV)
+            if tc:
+                scratch = torch.empty((kernels.sink_attn_tc_scratch(rows_q.shape[0], H, vd, splits),), dtype=torch.float32, device=DEV)
+                kernels.sink_attn_tc(rows_q, out, scratch, kc, vc, tk, sk, cos_v, sin_v, ctx, ctx.pages[0], H, G, dim, vd, window, 1.0, True, splits)
+            else:
+                kernels.sink_attn(rows_q, out, kc, vc, tk, sk, cos_v, sin_v, ctx, ctx.pages[0], H, G, dim, vd, window, 1.0, True)
+            assert int(ctx.status.item()) == 0
+            outs.append(out.float().cpu().numpy())
+        assert rel(outs[1], outs[0]) < 6e-3
+        return outs[0]
+
+    whole = both(ctx_for([T], [0], page_lists=[pages], n_pages=n_pages), bf(q.reshape(T, -1)), 1)
+    for i in range(star, last_in + 1):
+        assert rel(want, whole[i]) < 2e-2, i
+    for i in [star - 1] * (star > 0) + [first_out] * (first_out < T):
+        assert rel(want, whole[i]) > 0.3, i
+    for i in [last_in] + [first_out] * (first_out < T):
+        one = both(ctx_for([1], [0], starts=[i], page_lists=[pages], n_pages=n_pages, decode_splits=3), bf(q[i].reshape(1, -1)), 3)
+        assert (rel(want, one[0]) < 2e-2) == (i == last_in), i
+
+
 def _states(req, n_slots):
     return {k: torch.zeros((n_slots + 1, *r.shape), dtype=r.dtype, device=DEV) for k, r in req.items()}
 
