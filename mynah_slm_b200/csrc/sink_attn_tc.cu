@@ -18,6 +18,7 @@
 // Sums over keys run in ascending tiles whatever else is in the step; a query's result depends on its tile of 16
 // only through rounding-free zeros (masked weights are exactly zero).
 #include "layout.cuh"
+#include "mma_frag.cuh"
 
 namespace {
 
@@ -31,13 +32,7 @@ constexpr int MSTAGES_MAX = 8;        // stages of (K tile, queries) in flight, 
 constexpr int PS_LD = MKEYS + 8;      // row stride of the weights in shared memory (floats)
 static_assert(PAGE_TOKENS % MKEYS == 0, "a key tile lies inside a page");
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, bool valid) {
-    const int n = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(n));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+using namespace mmafrag;
 // waits until at most n of the newest groups are in flight (n below MSTAGES_MAX)
 __device__ __forceinline__ void cp_async_wait_upto(int n) {
     switch (n) {
@@ -50,23 +45,6 @@ __device__ __forceinline__ void cp_async_wait_upto(int n) {
         default: cp_async_wait<6>(); break;
     }
 }
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&h);
-}
 // m = hi + lo in two bfloat16 terms: hi is m cut off behind bfloat16's bits (a bit pattern, no rounding), lo the exact
 // remainder rounded to bfloat16, so hi + lo keeps 16 bits of m
 __device__ __forceinline__ void split_bf16(float m0, float m1, uint32_t& hi, uint32_t& lo) {
@@ -74,8 +52,6 @@ __device__ __forceinline__ void split_bf16(float m0, float m1, uint32_t& hi, uin
     hi = __byte_perm(b0, b1, 0x7632);
     lo = pack_bf16(m0 - __uint_as_float(b0 & 0xffff0000u), m1 - __uint_as_float(b1 & 0xffff0000u));
 }
-// byte offset of the 16-byte chunk c of row r in a tile whose rows hold CH chunks
-template <int CH> __device__ __forceinline__ int swz(int r, int c) { return (r * CH + (c ^ (r & 7))) * 16; }
 
 struct SinkTcArgs {
     int B, H, G, T, window, splits, interleaved, n_pos_v, stages, cg;
