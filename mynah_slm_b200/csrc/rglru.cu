@@ -48,14 +48,28 @@ template <typename TW>
 __global__ void __launch_bounds__(GT_THREADS)
 rglru_gates_kernel(const float* __restrict__ u, const TW* __restrict__ ra, const TW* __restrict__ ri, VecRef ba, VecRef bi,
                    VecRef lam, float decay_scale, float* __restrict__ a_out, float* __restrict__ b_out, int T, int width,
-                   int bw) {
-    extern __shared__ float us[];                                // [GT_ROWS][bw]
+                   int bw, int staged) {
+    extern __shared__ float us[];                                // [GT_ROWS][bw], then (staged) both matrices [k][bw + 1]
     griddep_wait();
     const int blk = blockIdx.y, t0 = blockIdx.x * GT_ROWS;
     const int nt = min(GT_ROWS, T - t0);
     for (int i = threadIdx.x; i < GT_ROWS * bw; i += GT_THREADS) {
         const int tt = i / bw, c = i % bw;
         us[i] = tt < nt ? u[(size_t)(t0 + tt) * width + (size_t)blk * bw + c] : 0.f;
+    }
+    // small blocks: both matrices pass through shared memory, read along their rows (coalesced) and laid down by k, so
+    // that a thread finds its output's weight of k beside its neighbours'; the sums keep their order
+    const int ldw = bw + 1;
+    float* ws1 = us + GT_ROWS * bw;
+    float* ws2 = ws1 + bw * ldw;
+    if (staged) {
+        const TW* m1 = ra + (size_t)blk * bw * bw;
+        const TW* m2 = ri + (size_t)blk * bw * bw;
+        for (int i = threadIdx.x; i < bw * bw; i += GT_THREADS) {
+            const int o = i / bw, k = i % bw;
+            ws1[k * ldw + o] = to_f32(m1[i]);
+            ws2[k * ldw + o] = to_f32(m2[i]);
+        }
     }
     __syncthreads();
     for (int o = threadIdx.x; o < bw; o += GT_THREADS) {
@@ -65,7 +79,7 @@ rglru_gates_kernel(const float* __restrict__ u, const TW* __restrict__ ra, const
 #pragma unroll
         for (int tt = 0; tt < GT_ROWS; tt++) ar[tt] = ai[tt] = 0.f;
         for (int k = 0; k < bw; k++) {
-            const float w1 = to_f32(wr[k]), w2 = to_f32(wi[k]);
+            const float w1 = staged ? ws1[k * ldw + o] : to_f32(wr[k]), w2 = staged ? ws2[k * ldw + o] : to_f32(wi[k]);
 #pragma unroll
             for (int tt = 0; tt < GT_ROWS; tt++) {
                 const float uv = us[tt * bw + k];
@@ -187,7 +201,9 @@ MYNAH_API int mynah_rglru_gates(const float* u, const void* ra, const void* ri, 
     MYNAH_REQUIRE(T > 0 && width > 0 && blocks > 0 && width % blocks == 0, "rglru_gates: bad sizes T=%d width=%d blocks=%d", T, width, blocks);
     MYNAH_REQUIRE(blocks <= 65535, "rglru_gates: %d blocks exceed one launch", blocks);
     const int bw = width / blocks;
-    const size_t smem = sizeof(float) * GT_ROWS * bw;
+    const size_t with_weights = sizeof(float) * ((size_t)GT_ROWS * bw + 2 * (size_t)bw * (bw + 1));
+    const int staged = with_weights <= 96 * 1024 ? 1 : 0;
+    const size_t smem = staged ? with_weights : sizeof(float) * GT_ROWS * bw;
     MYNAH_REQUIRE(smem <= 200 * 1024, "rglru_gates: blocks of %d channels exceed shared memory", bw);
     const dim3 grid(ceil_div(T, GT_ROWS), blocks);
     const VecRef b1{ba, v_dtype}, b2{bi, v_dtype}, lm{lam, v_dtype};
@@ -195,7 +211,7 @@ MYNAH_API int mynah_rglru_gates(const float* u, const void* ra, const void* ri, 
     if (smem > 48 * 1024 && cudaFuncSetAttribute(rglru_gates_kernel<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) \
         return mynah_fail("rglru_gates: %zu bytes of shared memory are not to be had", smem);                              \
     mynah_launch(rglru_gates_kernel<TW>, grid, dim3(GT_THREADS), smem, stream, u, (const TW*)ra, (const TW*)ri, b1, b2, lm,    \
-                 decay_scale, a_out, b_out, T, width, bw)
+                 decay_scale, a_out, b_out, T, width, bw, staged)
     if (w_dtype == MYNAH_F32) { GATES_LAUNCH(float); }
     else if (w_dtype == MYNAH_BF16) { GATES_LAUNCH(bf16); }
     else return mynah_fail("rglru_gates: unsupported dtype %d", w_dtype);
