@@ -162,6 +162,7 @@ class GroupPlan:
     window: Optional[int]          # None: every position is kept
     entries: list[int] = field(default_factory=list)    # schedule indices stored here
     v_head_dim: Optional[int] = None                     # width of the values; None: head_dim; 0: keys only
+    v_heads: Optional[int] = None                        # value heads; None: kv_heads
 
 
 class _Lengths:

@@ -2,7 +2,8 @@
 
 Per storage group: the keys of every entry of the group, each [n_pages,
 kv_heads, 64, head_dim] in the run's type, in one allocation, and the values
-likewise with their own width (a group whose mixers keep one vector per
+likewise with their own width and, where several key heads share a value
+head, their own number of heads (a group whose mixers keep one vector per
 position has none). Beside them: the fixed-size per-sequence state of the
 entries that ask for one, [max_seqs + 1, *shape]: a sequence's row is zeroed
 whenever its slot is handed out; the last row belongs to no sequence and is
@@ -31,7 +32,8 @@ class Cache:
             n = max(len(g.entries), 1)
             vd = g.head_dim if g.v_head_dim is None else g.v_head_dim
             self.keys.append(torch.empty((n, n_pages, g.kv_heads, PAGE_TOKENS, g.head_dim), dtype=dtype, device=device))
-            self.values.append(torch.empty((n, n_pages, g.kv_heads, PAGE_TOKENS, vd), dtype=dtype, device=device) if vd else None)
+            vh = g.kv_heads if getattr(g, "v_heads", None) is None else g.v_heads
+            self.values.append(torch.empty((n, n_pages, vh, PAGE_TOKENS, vd), dtype=dtype, device=device) if vd else None)
         self._state_tensors: list[torch.Tensor] = []
 
         def make(req):

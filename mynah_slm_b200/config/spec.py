@@ -13,7 +13,9 @@ more than once (each run then has a cache of its own), an entry may read
 the cache that an earlier entry wrote instead of keeping one, and an entry may
 ask for the embedding's output to be added to the stream once more before it
 runs (models that pass a range of layers several times feed the input back in
-at the start of every further pass).
+at the start of every further pass), or for one of the model's learned
+vectors to be added to every row of the stream before it runs (a vector per
+pass).
 """
 from __future__ import annotations
 
@@ -49,6 +51,8 @@ class ScheduleEntry:
     layer: int                          # index into ModelSpec.layers
     cache_from: Optional[int] = None    # schedule index whose cache this run reads, or None: its own
     add_embedding: bool = False         # the embedding's output is added to the stream right before this run
+    add_vector: Optional[int] = None    # row of the model's `stream_vectors` that is added to every row of the stream
+                                        # right before this run (a learned vector per pass of a looped range)
 
 
 @dataclass(frozen=True)
@@ -62,6 +66,8 @@ class ModelSpec:
     embedding: PartSpec             # token embedding (tensor name in params)
     final_norm: PartSpec
     head: PartSpec                  # output head; params["tied"] selects the embedding matrix
+    stream_vectors: Optional[PartSpec] = None   # params: name, count, dim: a tensor [count, dim] of vectors that
+                                                # schedule entries add to the stream (`add_vector`)
     eos_token_ids: tuple[int, ...] = ()
     sampling_defaults: Mapping[str, Any] = field(default_factory=dict)
 
@@ -72,6 +78,9 @@ class ModelSpec:
         for i, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
                 raise ConfigError(f"schedule[{i}] names layer {e.layer}, the model has {len(self.layers)}")
+            if e.add_vector is not None and (self.stream_vectors is None
+                                             or not 0 <= e.add_vector < int(self.stream_vectors["count"])):
+                raise ConfigError(f"schedule[{i}] adds vector {e.add_vector}, which the model does not have")
             if e.cache_from is not None:
                 if not 0 <= e.cache_from < i:
                     raise ConfigError(f"schedule[{i}] reads the cache of entry {e.cache_from}, which does not run before it")

@@ -33,7 +33,29 @@ struct DecodeArgs {
     float scale;
     int VD;              // width of a value head
     int chunk;           // 0: none; C: the query at position p sees keys from floor(p / C) * C on
+    float softcap;       // 0: none; c: score <- c * tanh(score / c), after the scale
+    int keep_first;      // with a window: keys at positions below it stay visible whatever their distance
+    int vdiv;            // kv head g reads value head g / vdiv
 };
+
+// The pages that the query of a sequence of `hi` positions can see: pages [pg0, pg1) of the window (or of everything),
+// and before them `nf` pages that hold kept first tokens and lie wholly outside it. `lo`: first position of the window.
+struct VisiblePages {
+    int lo, pg0, pg1, nf;
+    __device__ __forceinline__ int count() const { return nf + pg1 - pg0; }
+    // logical page of split s, or -1
+    __device__ __forceinline__ int page(int s) const { return s < nf ? s : (pg0 + s - nf < pg1 ? pg0 + s - nf : -1); }
+};
+__device__ __forceinline__ VisiblePages visible_pages(int hi, int window, int chunk, int keep_first) {
+    VisiblePages v{0, 0, 0, 0};
+    if (hi <= 0) return v;
+    if (window > 0) v.lo = max(0, hi - window);
+    if (chunk > 0) v.lo = max(v.lo, ((hi - 1) / chunk) * chunk);
+    v.pg0 = v.lo / PAGE_TOKENS;
+    v.pg1 = (hi - 1) / PAGE_TOKENS + 1;
+    if (window > 0 && keep_first > 0) v.nf = min((keep_first + PAGE_TOKENS - 1) / PAGE_TOKENS, v.pg0);
+    return v;
+}
 
 template <int GT>
 struct HeadState {
@@ -58,21 +80,21 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
 
     // key range of this split: the s-th page of the visible range
     const int hi = kv_len[b];
-    int lo = 0;
-    if (a.window > 0) lo = max(0, hi - a.window);
-    if (a.chunk > 0 && hi > 0) lo = max(lo, ((hi - 1) / a.chunk) * a.chunk);
+    const VisiblePages vp = visible_pages(hi, a.window, a.chunk, a.keep_first);
+    const int lo = vp.lo;
+    const int first_end = (a.window > 0 && a.keep_first > 0) ? a.keep_first : 0;   // keys below it are seen whatever `lo`
     int key_begin = 0, key_end = 0;
     if (hi > 0) {
-        const int pg0 = lo / PAGE_TOKENS, pg1 = (hi - 1) / PAGE_TOKENS + 1;
-        if (pg1 - pg0 > a.S) {                         // the launch is too small for this sequence: say so
+        if (vp.count() > a.S) {                        // the launch is too small for this sequence: say so
             if (threadIdx.x == 0 && s == 0) atomicOr(status, MYNAH_ST_SPLIT_RANGE);
         }
-        const int mp = pg0 + s;
-        if (mp < pg1) {
-            key_begin = max(lo, mp * PAGE_TOKENS);
+        const int mp = vp.page(s);
+        if (mp >= 0) {
+            key_begin = mp * PAGE_TOKENS < first_end ? mp * PAGE_TOKENS : max(lo, mp * PAGE_TOKENS);
             key_end = min(hi, (mp + 1) * PAGE_TOKENS);
         }
     }
+    const int KVV = a.KV / a.vdiv, gv = g / a.vdiv;
 
     float qv[GT][8];
 #pragma unroll
@@ -95,7 +117,7 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
     bool bad_page = false;
     for (int base = key_begin + warp * kpw; base < key_end; base += WARPS * kpw) {
         const int key = base + slot;
-        const bool valid = key < key_end;
+        const bool valid = key < key_end && (key >= lo || key < first_end);
         float kf[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, vf[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         bool have = false;
         if (valid) {
@@ -107,7 +129,8 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
             } else {
                 const size_t tok = ((size_t)page * a.KV + g) * PAGE_TOKENS + key % PAGE_TOKENS;
                 if (lane_on) load8(k_cache + tok * HD + u * 8, kf);
-                if (lane_on_v) load8(v_cache + tok * VD + u * 8, vf);
+                const size_t vtok = ((size_t)page * KVV + gv) * PAGE_TOKENS + key % PAGE_TOKENS;
+                if (lane_on_v) load8(v_cache + vtok * VD + u * 8, vf);
             }
             have = page >= 0;
         }
@@ -118,7 +141,8 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
             for (int j = 0; j < 8; j++) d = fmaf(qv[i][j], kf[j], d);
             for (int o = lpk >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
             if (have) {
-                const float sc = d * a.scale;
+                float sc = d * a.scale;
+                if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
                 const float m_new = fmaxf(st.m[i], sc);
                 const float alpha = expf(st.m[i] - m_new);
                 const float p = expf(sc - m_new);
@@ -189,14 +213,12 @@ attn_decode_split_kernel(const T* __restrict__ q, const T* __restrict__ k_cache,
 template <typename T>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            T* __restrict__ out, const int* __restrict__ kv_len, int window, int chunk,
-                                           int H, int HD, int S_max, int ldo) {
+                                           int keep_first, int H, int HD, int S_max, int ldo) {
     const int h = blockIdx.x, b = blockIdx.y;
     const size_t row0 = ((size_t)b * H + h) * S_max;
     // only the pages the sequence can see have partial results
     const int hi = kv_len[b];
-    int lo = window > 0 ? max(0, hi - window) : 0;
-    if (chunk > 0 && hi > 0) lo = max(lo, ((hi - 1) / chunk) * chunk);
-    const int S = hi > 0 ? min(S_max, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;
+    const int S = min(S_max, visible_pages(hi, window, chunk, keep_first).count());
     float mn = -INFINITY;
     for (int s = 0; s < S; s++) mn = fmaxf(mn, part_ml[(row0 + s) * 2]);
     float ls = 0.f;
@@ -234,7 +256,7 @@ int launch_decode(const void* q, void* out, int B, const DecodeArgs& a, const vo
         attn_decode_split_kernel<T, 4><<<grid, WARPS * 32, 0, stream>>>(qp, kp, vp, kv_len, pt, a, part_o, part_ml, status);
     if (mynah_check_launch("attn_decode_split")) return -1;
     const int threads = a.VD >= 128 ? 128 : (a.VD >= 64 ? 64 : 32);
-    attn_decode_combine_kernel<T><<<dim3(a.H, B), threads, 0, stream>>>(part_o, part_ml, (T*)out, kv_len, a.window, a.chunk, a.H, a.VD, a.S, a.ldo);
+    attn_decode_combine_kernel<T><<<dim3(a.H, B), threads, 0, stream>>>(part_o, part_ml, (T*)out, kv_len, a.window, a.chunk, a.keep_first, a.H, a.VD, a.S, a.ldo);
     return mynah_check_launch("attn_decode_combine");
 }
 
@@ -266,12 +288,33 @@ MYNAH_API int mynah_attn_decode(
                                 page_base, n_pages, window, 0, 0.f, n_splits, scratch, status, stream);
 }
 
+// The same with capped scores (softcap c > 0: score <- c tanh(score / c)), first tokens that a window keeps
+// (keep_first) and several key heads on one value head (the value cache has KV / vdiv heads).
+MYNAH_API int mynah_attn_decode_capped(
+    const void* q, void* out, int dtype, int B, int H, int KV, int HD, int VD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, float softcap, int keep_first, int vdiv, int n_splits, float* scratch, int* status,
+    cudaStream_t stream);
+
 MYNAH_API int mynah_attn_decode_ex(
     const void* q, void* out, int dtype, int B, int H, int KV, int HD, int VD, int ldq, int ldo,
     const void* k_cache, const void* v_cache, const int* kv_len,
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
     int window, int chunk, float scale, int n_splits, float* scratch, int* status, cudaStream_t stream) {
+    return mynah_attn_decode_capped(q, out, dtype, B, H, KV, HD, VD, ldq, ldo, k_cache, v_cache, kv_len, page_indptr, page_ids,
+                                    page_base, n_pages, window, chunk, scale, 0.f, 0, 1, n_splits, scratch, status, stream);
+}
+
+MYNAH_API int mynah_attn_decode_capped(
+    const void* q, void* out, int dtype, int B, int H, int KV, int HD, int VD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, float softcap, int keep_first, int vdiv, int n_splits, float* scratch, int* status,
+    cudaStream_t stream) {
     if (B == 0) return 0;
+    MYNAH_REQUIRE(softcap >= 0.f && keep_first >= 0 && vdiv >= 1 && KV % vdiv == 0, "attn_decode: bad cap, kept tokens or value sharing");
+    MYNAH_REQUIRE(keep_first == 0 || chunk == 0, "attn_decode: kept first tokens and a chunk mask do not go together");
     MYNAH_REQUIRE(B > 0 && H > 0 && KV > 0 && HD > 0 && H % KV == 0, "attn_decode: bad sizes B=%d H=%d KV=%d HD=%d", B, H, KV, HD);
     MYNAH_REQUIRE(HD % 8 == 0 && HD <= 256, "attn_decode: head_dim %d must be a multiple of 8 and at most 256", HD);
     MYNAH_REQUIRE(VD > 0 && VD % 8 == 0 && VD <= 256, "attn_decode: a value head of %d must be a multiple of 8 and at most 256", VD);
@@ -282,7 +325,7 @@ MYNAH_API int mynah_attn_decode_ex(
     MYNAH_REQUIRE(scratch != nullptr, "attn_decode: no scratch memory given");
     int lpk = 1;
     while (lpk * 8 < HD || lpk * 8 < VD) lpk <<= 1;
-    const DecodeArgs a{H, KV, HD, ldq, ldo, window, n_splits, lpk, scale != 0.f ? scale : 1.0f / sqrtf((float)HD), VD, chunk};
+    const DecodeArgs a{H, KV, HD, ldq, ldo, window, n_splits, lpk, scale != 0.f ? scale : 1.0f / sqrtf((float)HD), VD, chunk, softcap, keep_first, vdiv};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)B * H * n_splits * VD;

@@ -30,6 +30,9 @@ struct PrefillArgs {
     float scale;
     int VD;                     // width of a value head (HD unless the mixer's values are narrower or wider)
     int chunk;                  // 0: none; C: a query at position p sees keys from floor(p / C) * C on
+    float softcap;              // 0: none; c: score <- c * tanh(score / c), after the scale
+    int keep_first;             // with a window: keys at positions below it stay visible whatever their distance
+    int vdiv;                   // kv head g reads value head g / vdiv (1 unless several key heads share one value head)
 };
 
 template <typename TA, typename TC>
@@ -74,8 +77,15 @@ attn_prefill_generic_kernel(const TA* __restrict__ q, TA* __restrict__ out,
     if (a.window > 0) k_lo = max(0, p_first - a.window + 1);
     if (a.chunk > 0) k_lo = max(k_lo, (p_first / a.chunk) * a.chunk);
     k_lo = (k_lo / KT) * KT;
+    // kept first tokens: the tiles below `first_end` are walked too, the ones between them and the window skipped
+    const int first_end = (a.window > 0 && a.keep_first > 0) ? a.keep_first : 0;
+    const int KVV = a.KV / a.vdiv, vh = kvh / a.vdiv;
 
-    for (int kt = k_lo; kt <= p_last; kt += KT) {
+    for (int kt = first_end > 0 ? 0 : k_lo; kt <= p_last; kt += KT) {
+        if (kt >= first_end && kt < k_lo) {            // uniform over the CTA
+            kt = k_lo - KT;
+            continue;
+        }
         __syncthreads();                               // previous tile consumed; Qs written (first pass)
         const int page = page_of(pt, b, kt);
         if (page < 0) {
@@ -83,7 +93,7 @@ attn_prefill_generic_kernel(const TA* __restrict__ q, TA* __restrict__ out,
             return;                                    // uniform over the CTA
         }
         const size_t base = (((size_t)page * a.KV + kvh) * PAGE_TOKENS + kt % PAGE_TOKENS) * HD;
-        const size_t vbase = (((size_t)page * a.KV + kvh) * PAGE_TOKENS + kt % PAGE_TOKENS) * VD;
+        const size_t vbase = (((size_t)page * KVV + vh) * PAGE_TOKENS + kt % PAGE_TOKENS) * VD;
         const int n_keys = min(KT, n_kv - kt);         // rows past the sequence's end are not read
         for (int i = threadIdx.x; i < KT * HD; i += blockDim.x) {
             const int j = i / HD, d = i % HD;
@@ -104,9 +114,11 @@ attn_prefill_generic_kernel(const TA* __restrict__ q, TA* __restrict__ out,
             float dot = 0.f;
             for (int d = 0; d < HD; d++) dot = fmaf(qrow[d], krow[d], dot);
             bool vis = key <= p && key < n_kv;
-            if (a.window > 0) vis = vis && key > p - a.window;
+            if (a.window > 0) vis = vis && (key > p - a.window || key < a.keep_first);
             if (a.chunk > 0) vis = vis && key >= (p / a.chunk) * a.chunk;
-            const float s = vis ? dot * a.scale : -INFINITY;
+            float sc = dot * a.scale;
+            if (a.softcap > 0.f) sc = a.softcap * tanhf(sc / a.softcap);
+            const float s = vis ? sc : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(s));
             if (m_new == -INFINITY) continue;          // no visible key yet (uniform)
             const float alpha = expf(m[i] - m_new);    // exp(-inf) = 0 on the first tile
@@ -150,6 +162,14 @@ MYNAH_API int mynah_attn_prefill_generic_ex(
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
     int window, int chunk, float scale, int* status, cudaStream_t stream);
 
+// The same with capped scores (softcap c > 0: score <- c tanh(score / c)), first tokens that a window keeps
+// (keep_first) and several key heads on one value head (the value cache has KV / vdiv heads).
+MYNAH_API int mynah_attn_prefill_generic_capped(
+    const void* q, void* out, int dtype, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int VD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, float softcap, int keep_first, int vdiv, int* status, cudaStream_t stream);
+
 // q: [T, ldq] with head h at columns [h*HD, (h+1)*HD); out: [T, ldo] likewise.
 MYNAH_API int mynah_attn_prefill_generic(
     const void* q, void* out, int dtype, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
@@ -166,14 +186,26 @@ MYNAH_API int mynah_attn_prefill_generic_ex(
     const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
     int window, int chunk, float scale, int* status, cudaStream_t stream) {
+    return mynah_attn_prefill_generic_capped(q, out, dtype, n_tokens, B, max_q_len, H, KV, HD, VD, ldq, ldo, k_cache, v_cache,
+                                             cu_q, kv_len, page_indptr, page_ids, page_base, n_pages, window, chunk, scale,
+                                             0.f, 0, 1, status, stream);
+}
+
+MYNAH_API int mynah_attn_prefill_generic_capped(
+    const void* q, void* out, int dtype, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int VD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, float softcap, int keep_first, int vdiv, int* status, cudaStream_t stream) {
     if (B == 0 || max_q_len == 0) return 0;
+    MYNAH_REQUIRE(softcap >= 0.f && keep_first >= 0 && vdiv >= 1 && KV % vdiv == 0, "attn_prefill: bad cap, kept tokens or value sharing");
+    MYNAH_REQUIRE(keep_first == 0 || chunk == 0, "attn_prefill: kept first tokens and a chunk mask do not go together");
     MYNAH_REQUIRE(B > 0 && H > 0 && KV > 0 && HD > 0 && H % KV == 0, "attn_prefill: bad sizes B=%d H=%d KV=%d HD=%d", B, H, KV, HD);
     MYNAH_REQUIRE(HD <= 32 * MAXC, "attn_prefill: head_dim %d exceeds %d", HD, 32 * MAXC);
     MYNAH_REQUIRE(VD > 0 && VD <= 32 * MAXC, "attn_prefill: value head of %d lies outside 1..%d", VD, 32 * MAXC);
     MYNAH_REQUIRE(chunk >= 0, "attn_prefill: negative chunk");
     MYNAH_REQUIRE(H <= 65535, "attn_prefill: H=%d exceeds one launch", H);
     MYNAH_REQUIRE(window >= 0, "attn_prefill: negative window");
-    const PrefillArgs a{B, H, KV, HD, ldq, ldo, window, scale != 0.f ? scale : 1.0f / sqrtf((float)HD), VD, chunk};
+    const PrefillArgs a{B, H, KV, HD, ldq, ldo, window, scale != 0.f ? scale : 1.0f / sqrtf((float)HD), VD, chunk, softcap, keep_first, vdiv};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     const size_t smem = sizeof(float) * ((size_t)KT * (HD + 1) + (size_t)KT * VD + (size_t)QT * HD);
     (void)max_q_len;

@@ -204,6 +204,22 @@ MYNAH_API int mynah_residual_add(float* x, const void* delta, int act_dtype, lon
     return mynah_check_launch("residual_add");
 }
 
+// x[t][:] += v[:] for every row: one learned vector added to the whole stream (fp32).
+__global__ void residual_add_row_kernel(float* __restrict__ x, const float* __restrict__ v, size_t n, int D) {
+    griddep_launch();
+    griddep_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += v[i % D];
+}
+
+MYNAH_API int mynah_residual_add_row(float* x, const float* v, long long n_rows, int D, cudaStream_t stream) {
+    if (n_rows == 0) return 0;
+    MYNAH_REQUIRE(n_rows > 0 && D > 0, "residual_add_row: bad sizes");
+    const long long n = n_rows * D;
+    mynah_launch(residual_add_row_kernel, dim3((unsigned)ceil_div_ll(n, 256)), dim3(256), 0, stream, x, v, (size_t)n, D);
+    return mynah_check_launch("residual_add_row");
+}
+
 // ----------------------------------------------------------------- SwiGLU
 // a = (g * sigmoid(g)) * u with the sigmoid that never exponentiates a
 // positive argument (mynah-slm src/kernels.c:193-205). gate_up is [T, 2F]:

@@ -19,6 +19,12 @@
 //   act: plain    y = gelu(W_up,e h) (the exact, erf form), one matrix an expert, no gate
 //   moe_combine   out[t] = sum over the token's pairs of weight_pair * row
 //
+// A third way to pick (the group-limited scored router), with the clamped-gate experts:
+//   moe_group_router  scores s = sigmoid(W_r h) in fp32; the choice goes by s + correction; the experts form equal groups
+//                 of neighbours, a group counts the sum of its two largest choice scores, only experts of the `keep`
+//                 best groups can be chosen (the lower index wins every tie); the `top` largest choice scores among
+//                 them are the token's experts, and each counts s (without the correction) times a constant.
+//
 // The grid of the two products covers the most tiles a step can have (pairs / rows-per-tile + experts); CTAs
 // beyond the step's tiles leave at once, so a captured step needs no count from the host.
 #include "layout.cuh"
@@ -262,6 +268,97 @@ moe_router_kernel(const TA* __restrict__ h, const TA* __restrict__ w, VecRef bia
     }
     const float inv = 1.0f / sum;
     for (int k = lane; k < top; k += 32) pair_weight[t * top + k] *= inv;
+}
+
+// The group-limited scored router: one CTA a token; a warp an expert's logit at a time, then warp 0 picks.
+template <typename TA>
+__global__ void __launch_bounds__(ROUTER_THREADS)
+moe_group_router_kernel(const TA* __restrict__ h, const TA* __restrict__ w, VecRef correction, const int* __restrict__ tok_seq,
+                        int* __restrict__ choice, float* __restrict__ pair_weight, int D, int E, int top, int groups, int keep,
+                        float weight_scale) {
+    __shared__ float sc[MOE_MAX_EXPERTS], ch[MOE_MAX_EXPERTS], gs[MOE_MAX_EXPERTS];
+    griddep_wait();
+    const int t = blockIdx.x;
+    if (tok_seq[t] < 0) {
+        for (int k = threadIdx.x; k < top; k += blockDim.x) {
+            choice[t * top + k] = -1;
+            pair_weight[t * top + k] = 0.f;
+        }
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const TA* x = h + (size_t)t * D;
+    const int D8 = D % 8 == 0 ? D : 0;
+    for (int e = warp; e < E; e += ROUTER_THREADS / 32) {
+        const TA* wr = w + (size_t)e * D;
+        float acc = 0.f;
+#pragma unroll 2
+        for (int d = lane * 8; d < D8; d += 256) {
+            float xv[8], wv[8];
+            load8_f32(x + d, xv);
+            load8_f32(wr + d, wv);
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc = fmaf(xv[i], wv[i], acc);
+        }
+        for (int d = D8 + lane; d < D; d += 32) acc = fmaf(to_f32(x[d]), to_f32(wr[d]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            const float s = 1.0f / (1.0f + expf(-acc));
+            sc[e] = s;
+            ch[e] = s + correction.at(e);
+        }
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    if (keep < groups) {
+        const int per = E / groups;
+        for (int g = lane; g < groups; g += 32) {
+            float m1 = -INFINITY, m2 = -INFINITY;
+            for (int e = g * per; e < (g + 1) * per; e++) {
+                const float v = ch[e];
+                if (v > m1) { m2 = m1; m1 = v; }
+                else if (v > m2) m2 = v;
+            }
+            gs[g] = per > 1 ? m1 + m2 : m1;
+        }
+        __syncwarp();
+        // the best `keep` groups are marked by +inf in gs; the others' experts leave the choice
+        for (int k = 0; k < keep; k++) {
+            float best = -INFINITY;
+            int at = groups;
+            for (int g = lane; g < groups; g += 32)
+                if (gs[g] != INFINITY && gs[g] > best) { best = gs[g]; at = g; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            if (lane == 0 && at < groups) gs[at] = INFINITY;
+            __syncwarp();
+        }
+        for (int e = lane; e < E; e += 32)
+            if (gs[e / per] != INFINITY) ch[e] = -INFINITY;
+        __syncwarp();
+    }
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int at = E;
+        for (int e = lane; e < E; e += 32)
+            if (ch[e] > best) { best = ch[e]; at = e; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (lane == 0) {
+            choice[t * top + k] = at < E ? at : -1;
+            pair_weight[t * top + k] = at < E ? sc[at] * weight_scale : 0.f;
+            if (at < E) ch[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
 }
 
 // ---- the bfloat16 products on tensor cores (the core is in tile_mma.cuh) ----
@@ -578,4 +675,32 @@ MYNAH_API int mynah_moe_router_ffn(const void* h, int dtype, const int* tok_seq,
     if (mynah_check_launch("moe_router") != 0) return -1;
     return moe_run(h, dtype, nullptr, tok_seq, nullptr, choice, pair_weight, w_up, w_down, out, 1, y, o, ints, a_sorted, T, 1, top,
                    E, D, F, MOE_ACT_GELU, 0.f, 0.f, 1.0f, status, stream);
+}
+
+// The feed-forward with the group-limited scored router and the clamped-gate experts: scores sigmoid(W_r h) in fp32, the
+// choice by score + correction inside the `keep` best of `groups` equal groups of neighbouring experts, weights score *
+// weight_scale (not renormalised). w_router [E][D] in dtype, correction [E] in c_dtype; w_gu [E][2][F][D]; w_down [E][D][F];
+// out [T][D] in the activation type, or fp32 when out_f32. Scratch as for the learned router.
+MYNAH_API int mynah_moe_group_router_ffn(const void* h, int dtype, const int* tok_seq, const void* w_router, const void* correction,
+                                         int c_dtype, const void* w_gu, const void* w_down, void* out, int out_f32, void* y, float* o,
+                                         int* ints, void* a_sorted, int* choice, float* pair_weight, int T, int top, int E, int D,
+                                         int F, int groups, int keep, float weight_scale, float limit, float alpha, int* status,
+                                         cudaStream_t stream) {
+    if (T == 0) return 0;
+    MYNAH_REQUIRE(T > 0 && top > 0 && E > 0 && top <= E && D > 0 && F > 0, "moe_group_router_ffn: bad sizes");
+    MYNAH_REQUIRE(E <= MOE_MAX_EXPERTS, "moe_group_router_ffn: %d experts exceed %d", E, MOE_MAX_EXPERTS);
+    MYNAH_REQUIRE(groups >= 1 && E % groups == 0 && keep >= 1 && keep <= groups, "moe_group_router_ffn: %d experts do not form %d groups of which %d are kept", E, groups, keep);
+    MYNAH_REQUIRE(top <= keep * (E / groups), "moe_group_router_ffn: %d experts a token exceed those of %d kept groups", top, keep);
+    const VecRef corr{correction, c_dtype};
+    if (dtype == MYNAH_F32)
+        mynah_launch(moe_group_router_kernel<float>, dim3(T), dim3(ROUTER_THREADS), 0, stream, (const float*)h, (const float*)w_router,
+                     corr, tok_seq, choice, pair_weight, D, E, top, groups, keep, weight_scale);
+    else if (dtype == MYNAH_BF16)
+        mynah_launch(moe_group_router_kernel<bf16>, dim3(T), dim3(ROUTER_THREADS), 0, stream, (const bf16*)h, (const bf16*)w_router,
+                     corr, tok_seq, choice, pair_weight, D, E, top, groups, keep, weight_scale);
+    else
+        return mynah_fail("moe_group_router_ffn: unsupported dtype %d", dtype);
+    if (mynah_check_launch("moe_group_router") != 0) return -1;
+    return moe_run(h, dtype, nullptr, tok_seq, nullptr, choice, pair_weight, w_gu, w_down, out, out_f32, y, o, ints, a_sorted, T, 1,
+                   top, E, D, F, MOE_ACT_CLAMPED_GATE, limit, alpha, 1.0f, status, stream);
 }

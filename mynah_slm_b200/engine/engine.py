@@ -355,6 +355,8 @@ class Engine:
                 ahead.issue(self._layer_weights[i + 1])
             if e.add_embedding:
                 stream.add_f32(x0)
+            if e.add_vector is not None:
+                kernels.residual_add_row(stream.flush(), self.model.stream_vectors.rows[e.add_vector])
             self.model.layers[e.layer].forward(stream, ctx, views[i])
             if taps is not None:
                 taps[f"layer{i}"] = stream.flush().clone()
@@ -506,6 +508,8 @@ class Engine:
         for i, e in enumerate(self.model.schedule):
             if e.add_embedding:
                 stream.add_f32(x0)
+            if e.add_vector is not None:
+                kernels.residual_add_row(stream.flush(), self.model.stream_vectors.rows[e.add_vector])
             self.model.layers[e.layer].forward(stream, ctx, self.cache.views[i])
 
     def _embed(self, ctx: StepContext) -> torch.Tensor:

@@ -49,9 +49,15 @@ class Model:
             norms = {k: build_part("norm", v) for k, v in ls.norms.items()}
             self.layers.append(build_part("block", ls.block, mixer, ffn, norms))
         self.schedule = spec.schedule
+        self.stream_vectors = None
+        if spec.stream_vectors is not None:
+            from ..parts.embedding import StreamVectors
+            self.stream_vectors = StreamVectors(spec.stream_vectors)
 
     def parts(self) -> list[Part]:
         out: list[Part] = [self.embedding, self.final_norm, self.head]
+        if self.stream_vectors is not None:
+            out.append(self.stream_vectors)
         for block in self.layers:
             out.append(block)
             out.extend(block.parts())
@@ -78,10 +84,11 @@ class Model:
                 continue
             ep = EntryPlan(state=st, block_state=self.layers[e.layer].state_request())
             if kv is not None:
-                key = (kv.kv_heads, kv.head_dim, kv.window, kv.value_dim)
+                key = (kv.kv_heads, kv.head_dim, kv.window, kv.value_dim, kv.value_heads)
                 if key not in keys:
                     keys[key] = len(plan.groups)
-                    plan.groups.append(GroupPlan(kv.kv_heads, kv.head_dim, kv.window, v_head_dim=kv.value_dim))
+                    plan.groups.append(GroupPlan(kv.kv_heads, kv.head_dim, kv.window, v_head_dim=kv.value_dim,
+                                                 v_heads=kv.value_heads))
                 g = keys[key]
                 ep.group, ep.index_in_group = g, len(plan.groups[g].entries)
                 plan.groups[g].entries.append(i)

@@ -108,3 +108,23 @@ def decode_masked(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: 
         kernels.attn_decode_tc_masked(q, out, ctx, H, KV, HD, k_cache, v_cache, pages, window, chunk, scale, scratch)
         return
     kernels.attn_decode_general(q, out, ctx, H, KV, HD, VD, k_cache, v_cache, pages, window, chunk, scale, scratch)
+
+
+def prefill_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, VD: int, k_cache, v_cache, pages,
+                   window: int, scale: float, softcap: float, keep_first: int, vdiv: int) -> None:
+    """Prompt attention for mixers whose scores are capped, whose window keeps a sequence's first tokens, or whose
+    key heads share value heads (`vdiv` key heads a value head). Without any of the three it is `prefill_masked`."""
+    if not softcap and not keep_first and vdiv == 1:
+        prefill_masked(q, out, ctx, H, KV, HD, VD, k_cache, v_cache, pages, window, 0, scale)
+        return
+    kernels.attn_prefill_capped(q, out, ctx, H, KV, HD, VD, k_cache, v_cache, pages, window, scale, softcap, keep_first, vdiv)
+
+
+def decode_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, VD: int, k_cache, v_cache, pages,
+                  window: int, scale: float, softcap: float, keep_first: int, vdiv: int, scratch: torch.Tensor) -> None:
+    """The same choice for a decode step."""
+    if not softcap and not keep_first and vdiv == 1:
+        decode_masked(q, out, ctx, H, KV, HD, VD, k_cache, v_cache, pages, window, 0, scale, scratch)
+        return
+    kernels.attn_decode_capped(q, out, ctx, H, KV, HD, VD, k_cache, v_cache, pages, window, scale, softcap, keep_first, vdiv,
+                               scratch)

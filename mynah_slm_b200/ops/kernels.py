@@ -89,6 +89,15 @@ def residual_add(x: torch.Tensor, delta: torch.Tensor, scale: float = 1.0) -> No
     call("mynah_residual_add", ptr(x), ptr(delta), code(delta.dtype), x.numel(), float(scale), stream_ptr())
 
 
+def residual_add_row(x: torch.Tensor, v: torch.Tensor) -> None:
+    """x[t] += v for every row of the fp32 stream (one learned vector for the whole step)."""
+    _chk(x, "residual", torch.float32, 2)
+    _chk(v, "row", torch.float32, 1)
+    if v.numel() != x.shape[1]:
+        raise KernelError("residual_add_row: the row does not have the stream's width")
+    call("mynah_residual_add_row", ptr(x), ptr(v), x.shape[0], x.shape[1], stream_ptr())
+
+
 def swiglu(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _chk(gate_up, "gate_up", dim=2)
     T, F2 = gate_up.shape
@@ -1177,3 +1186,126 @@ def sink_attn_tc(q: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, k_ca
          code(talk.dtype), ptr(cos_v), ptr(sin_v), cos_v.shape[0], ptr(ctx.cu_q), ptr(ctx.kv_len), ptr(ctx.tok_seq),
          ptr(ctx.tok_pos), ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, T, ctx.B, H, G, dim, vd,
          int(window or 0), float(scale), 1 if interleaved else 0, int(splits), ptr(ctx.status), stream_ptr())
+
+
+# ------------------------------------------------------------------ capped / differential attention, gated heads
+def capped_attn_prep(qkv: torch.Tensor, q_out: torch.Tensor, Hq: int, Gk: int, Gv: int, dim: int, vd: int, dimp: int, vdp: int,
+                     maps: int, R: int, bias: Optional[torch.Tensor], q_gain: Optional[torch.Tensor],
+                     k_gain: Optional[torch.Tensor], eps: float, cos, sin, rot: int, interleaved: bool, ctx,
+                     pages: PageTableView, k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor]) -> None:
+    """Bias, per-unit RMS norm, rotation, packed queries and cache write of grouped-query attention with `maps`
+    score maps a head (csrc/capped_attn.cu). qkv: the projection's rows; q_out [T, Hq * dimp]."""
+    _rows(qkv, "capped_attn_prep: projection")
+    _chk(q_out, "packed queries", qkv.dtype, 2)
+    writes = k_cache is not None
+    need = Hq * dim + ((Gk * dim + Gv * vd) if writes else 0)
+    if qkv.shape[1] < need or q_out.shape[1] != Hq * dimp:
+        raise KernelError("capped_attn_prep: the rows do not fit the heads")
+    if bias is not None:
+        _chk(bias, "projection bias", torch.float32, 1)
+        if bias.numel() < need:
+            raise KernelError("capped_attn_prep: the bias is shorter than the projection")
+    gd = 0
+    if q_gain is not None:
+        if k_gain is None or q_gain.dtype != k_gain.dtype or q_gain.numel() != dim or k_gain.numel() != dim:
+            raise KernelError("capped_attn_prep: the two gains must have `dim` values of one dtype")
+        gd = code(q_gain.dtype)
+    if writes:
+        if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype:
+            raise KernelError("capped_attn_prep: the cache and the activations differ in dtype")
+        if tuple(k_cache.shape[1:]) != (Gk, PAGE_TOKENS, dimp) or tuple(v_cache.shape[1:]) != (Gv, PAGE_TOKENS, vdp):
+            raise KernelError("capped_attn_prep: the cache pages do not have the stored head sizes")
+    n_pos = cos.shape[0] if cos is not None else 0
+    if cos is not None and cos.shape[1] * 2 != rot:
+        raise KernelError("capped_attn_prep: the rotation table does not match the rotated dims")
+    call("mynah_capped_attn_prep", ptr(qkv), code(qkv.dtype), qkv.shape[0], qkv.stride(0), ptr(q_out), q_out.shape[1], Hq, Gk, Gv,
+         dim, vd, dimp, vdp, maps, R, ptr(bias), ptr(q_gain), ptr(k_gain), gd, float(eps), ptr(cos), ptr(sin),
+         rot if cos is not None else 0, 1 if interleaved else 0, n_pos, ptr(ctx.tok_seq), ptr(ctx.tok_pos),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, ptr(k_cache), ptr(v_cache), ptr(ctx.status),
+         stream_ptr())
+
+
+def attn_prefill_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, VD: int, k_cache, v_cache,
+                        pages: PageTableView, window: int, scale: float, softcap: float, keep_first: int, vdiv: int) -> None:
+    """The general prompt attention with capped scores, first tokens that the window keeps, and `vdiv` key heads on
+    one value head."""
+    _chk(q, "q", dim=2)
+    _chk(out, "attention output", q.dtype, 2)
+    call("mynah_attn_prefill_generic_capped", ptr(q), ptr(out), code(q.dtype), q.shape[0], ctx.B, ctx.max_q_len, H, KV, HD, VD,
+         q.shape[1], out.shape[1], ptr(k_cache), ptr(v_cache), ptr(ctx.cu_q), ptr(ctx.kv_len),
+         ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages, window or 0, 0, float(scale), float(softcap or 0.0),
+         int(keep_first or 0), int(vdiv), ptr(ctx.status), stream_ptr())
+
+
+def attn_decode_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, VD: int, k_cache, v_cache,
+                       pages: PageTableView, window: int, scale: float, softcap: float, keep_first: int, vdiv: int,
+                       scratch: torch.Tensor) -> None:
+    _chk(q, "q", dim=2)
+    _chk(out, "attention output", q.dtype, 2)
+    _chk(scratch, "scratch", torch.float32)
+    need = ctx.B * H * ctx.decode_splits * (VD + 2)
+    if scratch.numel() < need:
+        raise KernelError(f"attn_decode: scratch holds {scratch.numel()} floats, {need} are needed")
+    call("mynah_attn_decode_capped", ptr(q), ptr(out), code(q.dtype), ctx.B, H, KV, HD, VD, q.shape[1], out.shape[1],
+         ptr(k_cache), ptr(v_cache), ptr(ctx.kv_len), ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
+         window or 0, 0, float(scale), float(softcap or 0.0), int(keep_first or 0), int(vdiv), ctx.decode_splits,
+         ptr(scratch), ptr(ctx.status), stream_ptr())
+    lib.add_launches(1)        # pages and their combination
+
+
+def diff_combine(a: torch.Tensor, H: int, R: int, vd: int, vdp: int, lam: float, mult: float, eps: float, ctx) -> torch.Tensor:
+    """o_h = unit_rms(a_h,0 - lam * a_h,1) * mult, from the attention's slots (kv head, map, query head of the group) back
+    to head order; returns [T, H * vd] in the rows' type."""
+    _chk(a, "attention maps", dim=2)
+    if a.shape[1] != 2 * H * vdp:
+        raise KernelError("diff_combine: the rows do not hold two maps a head")
+    out = torch.empty((a.shape[0], H * vd), dtype=a.dtype, device=a.device)
+    call("mynah_diff_combine", ptr(a), code(a.dtype), a.shape[0], a.shape[1], ptr(out), out.shape[1], H, R, vd, vdp,
+         float(lam), float(mult), float(eps), ptr(ctx.tok_seq), stream_ptr())
+    return out
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, H: int, vd: int) -> torch.Tensor:
+    """x[t, h, :] *= sigmoid(gate[t, h]) in place; gate may be a column slice of wider rows."""
+    _chk(x, "heads", dim=2)
+    _rows(gate, "head_gate: gate")
+    if x.shape[1] != H * vd or gate.shape[1] < H or gate.dtype != x.dtype or gate.shape[0] != x.shape[0]:
+        raise KernelError("head_gate: the rows do not fit the heads")
+    call("mynah_head_gate", ptr(x), code(x.dtype), x.shape[0], x.shape[1], ptr(gate), gate.stride(0), H, vd, stream_ptr())
+    return x
+
+
+def moe_group_router_ffn(h: torch.Tensor, w_router: torch.Tensor, correction: torch.Tensor, w_gu: torch.Tensor,
+                         w_down: torch.Tensor, ctx, top: int, groups: int, keep: int, weight_scale: float, limit: float,
+                         alpha: float) -> torch.Tensor:
+    """Experts picked by sigmoid scores (fp32) with a correction for the choice, inside the `keep` best of `groups` groups of
+    neighbouring experts; clamped-gate experts; weights score * weight_scale (csrc/moe.cu). w_router [E, D], correction
+    [E], w_gu [E, 2, F, D], w_down [E, D, F]; returns [T, D] in the rows' type."""
+    _chk(h, "rows", dim=2)
+    _chk(w_router, "router weights", h.dtype, 2)
+    _chk(correction, "router correction", dim=1)
+    _chk(w_gu, "gate/up weights", h.dtype, 4)
+    _chk(w_down, "down weights", h.dtype, 3)
+    T, D = h.shape
+    E, _, F, _ = w_gu.shape
+    if (tuple(w_gu.shape) != (E, 2, F, D) or tuple(w_down.shape) != (E, D, F) or tuple(w_router.shape) != (E, D)
+            or correction.numel() != E or not 1 <= top <= E):
+        raise KernelError("moe_group_router_ffn: sizes do not fit")
+    P_ = T * top
+    dev = h.device
+    grouped = int(lib.load().mynah_moe_grouped_rows(T, top, E, D, F, code(h.dtype)))
+    R = max(P_, grouped)
+    out = torch.empty((T, D), dtype=h.dtype, device=dev)
+    y = torch.empty((R, F), dtype=h.dtype, device=dev)
+    o = torch.empty((R, D), dtype=torch.float32, device=dev)
+    a = torch.empty((R, D), dtype=h.dtype, device=dev) if grouped else None
+    ints = torch.empty((3 * P_ + 1 + 3 * int(lib.load().mynah_moe_max_tiles(T, top, E)) + R + R // 128 + 1,),
+                       dtype=torch.int32, device=dev)
+    weights = torch.empty((P_,), dtype=torch.float32, device=dev)
+    choice = ints[ints.numel() - P_:]
+    call("mynah_moe_group_router_ffn", ptr(h), code(h.dtype), ptr(ctx.tok_seq), ptr(w_router), ptr(correction),
+         code(correction.dtype), ptr(w_gu), ptr(w_down), ptr(out), 0, ptr(y), ptr(o), ptr(ints), ptr(a), ptr(choice),
+         ptr(weights), T, top, E, D, F, int(groups), int(keep), float(weight_scale), float(limit), float(alpha),
+         ptr(ctx.status), stream_ptr())
+    lib.add_launches(5 if grouped else 4)     # router, route, (gather,) two products, combine
+    return out

@@ -128,6 +128,17 @@ _SIGNATURES: dict[str, list] = {
     "mynah_retention_prep": [P, c_int, c_int, c_int, c_int, P, P, c_int, c_int, c_int, P, P, c_int, c_int, c_int,
                              c_float, P, P, P, P],
     "mynah_retention_scan": [P, P, P, c_int, c_int, c_int, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
+    "mynah_attn_prefill_generic_capped": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          P, P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_float, c_int, c_int, P, P],
+    "mynah_attn_decode_capped": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_float, c_int, c_int, c_int, P, P, P],
+    "mynah_capped_attn_prep": [P, c_int, c_int, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                               P, P, P, c_int, c_float, P, P, c_int, c_int, c_int, P, P, P, P, P, c_int, P, P, P, P],
+    "mynah_diff_combine": [P, c_int, c_int, c_int, P, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, P, P],
+    "mynah_head_gate": [P, c_int, c_int, c_int, P, c_int, c_int, c_int, P],
+    "mynah_residual_add_row": [P, P, c_longlong, c_int, P],
+    "mynah_moe_group_router_ffn": [P, c_int, P, P, P, c_int, P, P, P, c_int, P, P, P, P, P, P, c_int, c_int, c_int, c_int,
+                                   c_int, c_int, c_int, c_float, c_float, c_float, P, P],
     "mynah_moe_table_ffn": [P, c_int, P, P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_float, c_float, c_float, P, P],
 }

@@ -11,6 +11,8 @@ rotated query/key dimensions, values of `vdim`, a latent of `kv_rank`:
   q_r (every head) and k_r are rotated (the position part's pairing, tables and scaling)
   per head:  k_u = W_uk c,  v = W_uv c,  score = (q_u . k_u + q_r . k_r) * scale
   causal softmax (within `window` when given), W_o on the concatenated heads
+  with `gate` (a tensor name): head h's output is multiplied by sigmoid(W_g h)_h first; W_g [H, hidden] reads the
+  same input as the projections
 
 The maps move to the query side (`csrc/latent_attn.cu`): q_a = W_uk^T q_u per
 head, the cache row of a position is [c | k_r] for ONE kv head, the library's
@@ -21,8 +23,8 @@ own queries, W_uk, W_uv and W_o.
 
 Parameters: hidden_size, heads, dim, rot_dim, vdim, kv_rank, eps, scale, window,
 rot (None or the parameters of a `rotary` position part), own_kv (False for a
-run that reads another's cache), and the tensors' names: q, dkv, dkv_norm, uk,
-uv, o.
+run that reads another's cache), gate (None, or the name of the output gate's
+matrix), and the tensors' names: q, dkv, dkv_norm, uk, uv, o.
 
 Cache rows are padded with zeros to a multiple of 8 values (the attention
 kernels' 16-byte loads).
@@ -53,6 +55,7 @@ class LatentAttention(Mixer):
         self.window: Optional[int] = spec.get("window")
         self.own_kv = bool(spec.get("own_kv", True))
         self.names = {k: str(spec[k]) for k in ("q", "dkv", "dkv_norm", "uk", "uv", "o")}
+        self.gate_name: Optional[str] = spec.get("gate")
         self.HDp = _pad8(self.r + self.rd)
         if self.HDp > kernels.MAX_HEAD_DIM:
             raise ConfigError(f"latent_attention: a cache row of {self.r} + {self.rd} values exceeds {kernels.MAX_HEAD_DIM}")
@@ -70,6 +73,8 @@ class LatentAttention(Mixer):
         specs = [TensorSpec(n["q"], (H * (self.dim + self.rd), D)),
                  TensorSpec(n["uk"], (H * self.dim, r)), TensorSpec(n["uv"], (H * self.vd, r)),
                  TensorSpec(n["o"], (D, H * self.vd))]
+        if self.gate_name:
+            specs.append(TensorSpec(self.gate_name, (H, D)))
         if self.own_kv:
             specs += [TensorSpec(n["dkv"], (r + self.rd, D)),
                       TensorSpec(n["dkv_norm"], (r,), role="gain", init="gain", std=0.1)]
@@ -79,15 +84,18 @@ class LatentAttention(Mixer):
         n = self.names
         wq = tensors[n["q"]]
         self.n_q = wq.shape[0]
+        parts = [wq]
         if self.own_kv:
-            parts = [wq, tensors[n["dkv"]]]
-            rows = self.n_q + self.r + self.rd
-            if rows % 8:
-                parts.append(torch.zeros((8 - rows % 8, self.D), dtype=wq.dtype, device=wq.device))
-            self.w_in = torch.cat(parts, dim=0).contiguous()
-            self.norm_w = tensors[n["dkv_norm"]]
-        else:
-            self.w_in, self.norm_w = wq, None
+            parts.append(tensors[n["dkv"]])
+        self.norm_w = tensors[n["dkv_norm"]] if self.own_kv else None
+        rows = sum(t.shape[0] for t in parts)
+        self.gate_off = rows                     # the gate's logits follow the projections in the same product
+        if self.gate_name:
+            parts.append(tensors[self.gate_name])
+            rows += self.H
+        if len(parts) > 1 and rows % 8:
+            parts.append(torch.zeros((8 - rows % 8, self.D), dtype=wq.dtype, device=wq.device))
+        self.w_in = torch.cat(parts, dim=0).contiguous() if len(parts) > 1 else wq
         # W_uk per head, transposed: q_a[r] = sum_i W_uk[h, i, r] q_u[i]
         self.w_ukT = tensors[n["uk"]].view(self.H, self.dim, self.r).transpose(1, 2).contiguous()
         self.w_uv = tensors[n["uv"]].view(self.H, self.vd, self.r).contiguous()
@@ -134,6 +142,8 @@ class LatentAttention(Mixer):
                                               self.scale)
         v = torch.empty((T, H * self.vd), dtype=p.dtype, device=p.device)
         kernels.head_linear(lat, HDp, 0, self.w_uv, v, self.vd, 0)
+        if self.gate_name:
+            kernels.head_gate(v, p[:, self.gate_off: self.gate_off + H], H, self.vd)
         return kernels.linear(v, self.w_o)
 
 

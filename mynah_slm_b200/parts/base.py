@@ -65,13 +65,20 @@ class KVRequest:
     `values` is False, values of kv_heads x v_head_dim (head_dim when None). A
     mixer that keeps one vector per position (a latent that serves as key and
     value) asks for values=False. window=None keeps every position; window=W
-    keeps the last W. Runs that ask for the same thing share a storage group
+    keeps the last W. A mixer whose key heads share value heads (several score
+    maps over the same values) gives the number of value heads in `v_heads`
+    (None: kv_heads). Runs that ask for the same thing share a storage group
     and its page lists."""
     kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     values: bool = True
+    v_heads: Optional[int] = None
+
+    @property
+    def value_heads(self) -> int:
+        return self.kv_heads if self.v_heads is None else self.v_heads
 
     @property
     def value_dim(self) -> int:

@@ -16,7 +16,7 @@ from typing import Mapping, Optional
 import torch
 
 from ..ops import kernels
-from .base import Embedding, Head, TensorSpec, register_embedding, register_head
+from .base import Embedding, Head, Part, TensorSpec, register_embedding, register_head
 
 
 class TokenEmbedding(Embedding):
@@ -90,3 +90,19 @@ class TokenPositionEmbedding(Embedding):
 
 
 register_embedding("token_position_embedding", TokenPositionEmbedding)
+
+
+class StreamVectors(Part):
+    """Learned vectors [count, dim] that the schedule adds to every row of the residual stream before chosen runs
+    (`ScheduleEntry.add_vector`); kept in fp32, like the stream. Parameters: name, count, dim."""
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.name, self.count, self.dim = str(spec["name"]), int(spec["count"]), int(spec["dim"])
+        self.rows = None
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return [TensorSpec(self.name, (self.count, self.dim), role="gain", init="normal", std=0.1)]
+
+    def bind(self, tensors, runtime) -> None:
+        self.rows = tensors[self.name].to(torch.float32).contiguous()

@@ -90,6 +90,8 @@ def _register_builtin() -> None:
     register_architecture(nedupel.ARCHITECTURE, nedupel.NedupelConfig.from_dict, replace=True)
     from .config import gupizen
     register_architecture(gupizen.ARCHITECTURE, gupizen.GupizenConfig.from_dict, replace=True)
+    from .config import gomuzen
+    register_architecture(gomuzen.ARCHITECTURE, gomuzen.GomuzenConfig.from_dict, replace=True)
 
 
 _register_builtin()
