@@ -48,6 +48,10 @@ struct PfArgs {
     int window;
     float scale_log2;                 // (1 / sqrt(head_dim)) * log2(e), or the caller's scale * log2(e)
     int chunk;                        // 0: none; C: the row at position p sees keys from floor(p / C) * C on
+    int keep_first;                   // with a window: keys at positions below it are seen whatever their distance (every
+                                      // page of the sequence must then be in the page list: nothing was given back)
+    int vdiv;                         // kv head g reads value head g / vdiv (the value cache has KV / vdiv heads)
+    float cap_in, cap_log2;           // capped scores (CAP kernels): c tanh(s scale / c) log2(e) = cap_log2 * tanh(s * cap_in / 2)
     // The first key that the row at position p sees. Window and chunk both give a bound that does not fall as p
     // grows, so a tile's first row has the tile's lowest bound and its last row the highest.
     __device__ __forceinline__ bool bounded() const { return window > 0 || chunk > 0; }
@@ -114,7 +118,12 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 
 // NS: stages of K, V and the scores. 2: a CTA an SM, the next tile's scores and operands under this tile's softmax.
 // 1: half the shared and tensor memory, so that two CTAs share an SM and one's softmax runs under the other's products.
-template <int HD, int NS>
+// A score in the base-2 domain under a cap: cap_log2 * tanh(s * cap_in / 2), with tanh(x) = 1 - 2 / (e^(2x) + 1).
+__device__ __forceinline__ float capped_log2(float s, float cap_in, float cap_log2) {
+    return s == -INFINITY ? -INFINITY : cap_log2 * (1.0f - __fdividef(2.0f, ex2(s * cap_in) + 1.0f));
+}
+
+template <int HD, int NS, bool CAP>
 __global__ void __launch_bounds__(THREADS, NS == 1 ? 2 : 1)
 attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ cu_q,
@@ -150,7 +159,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int rows_valid = min(BQ, n_q - q0);
     const int kt_hi = (past + q0 + rows_valid - 1) / BKV;      // tile of the last key that the last row sees
     const int kt_lo = a.bounded() ? a.row_lo(past + q0) / BKV : 0;
-    const int n_tiles = kt_hi - kt_lo + 1;
+    // Kept first tokens: the tiles that hold them and lie wholly before the window's first tile are walked first.
+    const int kf = a.window > 0 ? a.keep_first : 0;
+    const int nf = kf > 0 ? min((kf + BKV - 1) / BKV, kt_lo) : 0;
+    const int n_tiles = nf + kt_hi - kt_lo + 1;
+    auto tile_of = [&](int j) { return j < nf ? j : kt_lo + j - nf; };
+    const int KVV = a.KV / a.vdiv;
     const int lo_min = a.bounded() ? a.row_lo(past + q0) : 0;    // the first key that any row of the tile sees
     const int kvh = h / (a.H / a.KV);
 #ifdef MYNAH_ATTN_STAMPS
@@ -197,11 +211,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int j = 0; j < n_tiles; j++) {
                 const int st = stage_of(j);
                 const uint32_t prev_use = use_of(j) ^ 1;       // parity of the stage's use before this one
-                const int key0 = (kt_lo + j) * BKV;
+                const int key0 = tile_of(j) * BKV;
                 // A page is brought only if it holds a key that some row of the tile sees: the first page of the
                 // first tile may lie wholly before the window (a cache that keeps a window has given it back),
                 // the second page of the last tile beyond the sequence's end.
-                const bool need0 = key0 + PAGE_TOKENS > lo_min, need1 = key0 + PAGE_TOKENS < kvl;
+                const bool need0 = kf > 0 || key0 + PAGE_TOKENS > lo_min, need1 = key0 + PAGE_TOKENS < kvl;
                 const int p0 = need0 ? page_of(pt, b, key0) : -1;
                 const int p1 = need1 ? page_of(pt, b, key0 + PAGE_TOKENS) : -1;
                 if ((need0 && p0 < 0) || (need1 && p1 < 0) || (!need0 && !need1)) {
@@ -229,8 +243,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 mbar_expect_tx(v_full + 8 * st, bytes);
 #pragma unroll
                 for (int hf = 0; hf < HALVES; hf++) {
-                    if (p0 >= 0) tma_load_2d(smem_u32(vd + hf * HALF_BYTES), &map_v, hf * 64, (p0 * a.KV + kvh) * PAGE_TOKENS, v_full + 8 * st);
-                    if (p1 >= 0) tma_load_2d(smem_u32(vd + hf * HALF_BYTES + PAGE_BYTES), &map_v, hf * 64, (p1 * a.KV + kvh) * PAGE_TOKENS, v_full + 8 * st);
+                    if (p0 >= 0) tma_load_2d(smem_u32(vd + hf * HALF_BYTES), &map_v, hf * 64, (p0 * KVV + kvh / a.vdiv) * PAGE_TOKENS, v_full + 8 * st);
+                    if (p1 >= 0) tma_load_2d(smem_u32(vd + hf * HALF_BYTES + PAGE_BYTES), &map_v, hf * 64, (p1 * KVV + kvh / a.vdiv) * PAGE_TOKENS, v_full + 8 * st);
                 }
                 v_issued = j + 1;
             }
@@ -311,7 +325,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             const uint32_t use = use_of(j);
             const int xst = j & 1;                             // the exchange has two buffers whatever NS is
             const uint32_t xuse = (j >> 1) & 1;
-            const int key0 = (kt_lo + j) * BKV + grp * HALF_KEYS;     // this thread's first key
+            const int key0 = tile_of(j) * BKV + grp * HALF_KEYS;     // this thread's first key
             const uint32_t t_s = t_row + st * BKV;
             STAMP(j, 0);
             if (!warp_wait(s_full + 8 * st, use)) { ok = false; break; }
@@ -322,13 +336,14 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                                    (bounded && key0 < lo_max);
             const int hi = min(qpos, kvl - 1) - key0;          // the last of this thread's scores that its row sees
             const int lo = bounded ? lo_r - key0 : -(1 << 30);
+            const int kfr = kf - key0;                         // this thread's scores below it belong to kept first tokens
             // 32 of the thread's scores (the c-th half of them), those that the row must not see set to -inf
             auto fetch32 = [&](int c, float (&v)[32]) {
                 tc_ld32(t_s + grp * HALF_KEYS + c * 32, reinterpret_cast<uint32_t(&)[32]>(v));
                 if (need_mask) {                               // a compare with a constant and a select per score
                     if (bounded) {
 #pragma unroll
-                        for (int e = 0; e < 32; e++) v[e] = (c * 32 + e <= hi && c * 32 + e >= lo) ? v[e] : -INFINITY;
+                        for (int e = 0; e < 32; e++) v[e] = (c * 32 + e <= hi && (c * 32 + e >= lo || c * 32 + e < kfr)) ? v[e] : -INFINITY;
                     } else {
 #pragma unroll
                         for (int e = 0; e < 32; e++) v[e] = c * 32 + e <= hi ? v[e] : -INFINITY;
@@ -346,7 +361,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (need_mask) {
                     if (bounded) {
 #pragma unroll
-                        for (int e = 0; e < HALF_KEYS; e++) s[e] = (e <= hi && e >= lo) ? s[e] : -INFINITY;
+                        for (int e = 0; e < HALF_KEYS; e++) s[e] = (e <= hi && (e >= lo || e < kfr)) ? s[e] : -INFINITY;
                     } else {
 #pragma unroll
                         for (int e = 0; e < HALF_KEYS; e++) s[e] = e <= hi ? s[e] : -INFINITY;
@@ -373,7 +388,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (lane == 0) mbar_arrive(x_full + 8 * xst);
             if (!warp_wait(x_full + 8 * xst, xuse)) { ok = false; break; }
             STAMP(j, 4);
-            const float m_new = fmaxf(mx_own, xch[(xst * 2 + (grp ^ 1)) * BQ + row]) * a.scale_log2;
+            const float mx_row = fmaxf(mx_own, xch[(xst * 2 + (grp ^ 1)) * BQ + row]);
+            const float m_new = CAP ? capped_log2(mx_row, a.cap_in, a.cap_log2) : mx_row * a.scale_log2;
             // The reference maximum follows the true one lazily: while the row's maximum stays within 2^8 of it
             // nothing is rescaled (the probabilities just exceed one by up to that factor, which fp32 sums and
             // bf16 products carry without loss). Both threads of a row take the same decision.
@@ -405,7 +421,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int e = 0; e < HALF_KEYS; e += 2) {
                     float x0, x1;
-                    fma2(x0, x1, s[e], s[e + 1], a.scale_log2, -m_use);
+                    if constexpr (CAP) {
+                        x0 = capped_log2(s[e], a.cap_in, a.cap_log2) - m_use;
+                        x1 = capped_log2(s[e + 1], a.cap_in, a.cap_log2) - m_use;
+                    } else {
+                        fma2(x0, x1, s[e], s[e + 1], a.scale_log2, -m_use);
+                    }
                     const float p0 = ex2(x0), p1 = ex2(x1);                       // 2^-inf = 0
                     add2(sum4[e & 2], sum4[(e & 2) + 1], p0, p1);
                     pk[e >> 1] = pack2(p0, p1);
@@ -424,7 +445,12 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                     for (int e = 0; e < 32; e += 2) {
                         float x0, x1;
-                        fma2(x0, x1, v[e], v[e + 1], a.scale_log2, -m_use);
+                        if constexpr (CAP) {
+                            x0 = capped_log2(v[e], a.cap_in, a.cap_log2) - m_use;
+                            x1 = capped_log2(v[e + 1], a.cap_in, a.cap_log2) - m_use;
+                        } else {
+                            fma2(x0, x1, v[e], v[e + 1], a.scale_log2, -m_use);
+                        }
                         const float p0 = ex2(x0), p1 = ex2(x1);
                         add2(sum4[e & 2], sum4[(e & 2) + 1], p0, p1);
                         pk[e >> 1] = pack2(p0, p1);
@@ -438,8 +464,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             // Rows of V that were not brought (beyond the sequence's end, or a first page wholly before the window)
             // hold whatever was there: zero them, a probability of zero times a stale NaN would still be NaN.
-            const int tile_key0 = (kt_lo + j) * BKV;
-            const bool past_end = tile_key0 + BKV > kvl, before_window = tile_key0 + PAGE_TOKENS <= lo_min;
+            const int tile_key0 = tile_of(j) * BKV;
+            const bool past_end = tile_key0 + BKV > kvl, before_window = kf == 0 && tile_key0 + PAGE_TOKENS <= lo_min;
             if (past_end || before_window) {
                 if (!warp_wait(v_full + 8 * st, use)) { ok = false; break; }
                 if ((past_end && row >= kvl - tile_key0) || (before_window && row < PAGE_TOKENS)) {
@@ -499,11 +525,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #endif
 }
 
-template <int HD, int NS>
+template <int HD, int NS, bool CAP>
 int launch(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, int n_tokens, int B, int max_q_len, const int* cu_q,
            const int* kv_len, PageTable pt, PfArgs a, bf16* out, int* status, cudaStream_t stream) {
     constexpr size_t smem = (1 + 2 * NS) * (size_t)(HD / 64) * HALF_BYTES + 128 + 2 * 2 * BQ * sizeof(float) + 1024;
-    auto kern = attn_prefill_tcgen05_kernel<HD, NS>;
+    auto kern = attn_prefill_tcgen05_kernel<HD, NS, CAP>;
     static bool opted = false;
     if (!opted) {
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -567,14 +593,34 @@ MYNAH_API int mynah_attn_prefill_tcgen05(
                                          page_indptr, page_ids, page_base, n_pages, window, 0, 0.f, status, stream);
 }
 
+MYNAH_API int mynah_attn_prefill_tcgen05_capped(
+    const void* q, void* out, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, float softcap, int keep_first, int vdiv, int* status, cudaStream_t stream);
+
 // The same with a chunk mask beside the window (0: none) and a score scale given by the caller (0: 1/sqrt(HD)).
 MYNAH_API int mynah_attn_prefill_tcgen05_ex(
     const void* q, void* out, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
     const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
     int window, int chunk, float scale, int* status, cudaStream_t stream) {
+    return mynah_attn_prefill_tcgen05_capped(q, out, n_tokens, B, max_q_len, H, KV, HD, ldq, ldo, k_cache, v_cache, cu_q, kv_len,
+                                             page_indptr, page_ids, page_base, n_pages, window, chunk, scale, 0.f, 0, 1, status, stream);
+}
+
+// The same with capped scores (softcap c > 0: score <- c tanh(score / c), after the scale), first tokens that the window
+// keeps (keep_first; the page lists must then hold every page of a sequence) and `vdiv` key heads on one value head (the
+// value cache is [n_pages, KV / vdiv, 64, HD]).
+MYNAH_API int mynah_attn_prefill_tcgen05_capped(
+    const void* q, void* out, int n_tokens, int B, int max_q_len, int H, int KV, int HD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* cu_q, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window, int chunk, float scale, float softcap, int keep_first, int vdiv, int* status, cudaStream_t stream) {
     if (B == 0 || max_q_len == 0 || n_tokens == 0) return 0;
     MYNAH_REQUIRE(window >= 0 && chunk >= 0, "attn_prefill_tcgen05: negative window or chunk");
+    MYNAH_REQUIRE(softcap >= 0.f && keep_first >= 0 && vdiv >= 1 && KV % vdiv == 0 && (keep_first == 0 || chunk == 0),
+                  "attn_prefill_tcgen05: bad cap, kept tokens or value sharing");
     MYNAH_REQUIRE(mynah_attn_prefill_tcgen05_supported(H, KV, HD), "attn_prefill_tcgen05: H=%d KV=%d head_dim=%d is not taken by this kernel", H, KV, HD);
     MYNAH_REQUIRE(ldq % 8 == 0 && ldo % 8 == 0 && ((uintptr_t)q & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
                   ((uintptr_t)k_cache & 15) == 0 && ((uintptr_t)v_cache & 15) == 0,
@@ -584,8 +630,10 @@ MYNAH_API int mynah_attn_prefill_tcgen05_ex(
     CUtensorMap mq, mk, mv;
     if (make_map(&mq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, n_tokens, (long long)H * HD, ldq, BQ, 64)) return -1;
     if (make_map(&mk, k_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * KV * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
-    if (make_map(&mv, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * KV * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
-    const PfArgs a{B, H, KV, ldo, window, (scale != 0.f ? scale : 1.0f / sqrtf((float)HD)) * 1.4426950408889634f, chunk};
+    if (make_map(&mv, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * (KV / vdiv) * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
+    const float scale_used = scale != 0.f ? scale : 1.0f / sqrtf((float)HD);
+    const PfArgs a{B, H, KV, ldo, window, scale_used * 1.4426950408889634f, chunk, keep_first, vdiv,
+                   softcap > 0.f ? 2.0f * scale_used * 1.4426950408889634f / softcap : 0.f, softcap * 1.4426950408889634f};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     // Two CTAs an SM pay once there are several waves of CTAs (64 prompts of 2,048 tokens and 32 heads: 2.97 against
     // 3.34 ms; 4 prompts: 221 against 236 us); with one wave or two, the longest CTA's own chain sets the time and it
@@ -593,10 +641,14 @@ MYNAH_API int mynah_attn_prefill_tcgen05_ex(
     const int mode = stages_mode();
     const long long ctas = (long long)H * (ceil_div(n_tokens, BQ) + B);
     const int stages = mode != 0 ? mode : (ctas >= 8ll * mynah_sm_count() ? 1 : 2);
+#define PF_GO(HD_, NS_)                                                                                                         \
+    return softcap > 0.f ? launch<HD_, NS_, true>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream) \
+                         : launch<HD_, NS_, false>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream)
     if (stages == 1) {
-        if (HD == 128) return launch<128, 1>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
-        return launch<64, 1>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
+        if (HD == 128) PF_GO(128, 1);
+        PF_GO(64, 1);
     }
-    if (HD == 128) return launch<128, 2>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
-    return launch<64, 2>(mq, mk, mv, n_tokens, B, max_q_len, cu_q, kv_len, pt, a, (bf16*)out, status, stream);
+    if (HD == 128) PF_GO(128, 2);
+    PF_GO(64, 2);
+#undef PF_GO
 }

@@ -113,9 +113,15 @@ def decode_masked(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: 
 def prefill_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, VD: int, k_cache, v_cache, pages,
                    window: int, scale: float, softcap: float, keep_first: int, vdiv: int) -> None:
     """Prompt attention for mixers whose scores are capped, whose window keeps a sequence's first tokens, or whose
-    key heads share value heads (`vdiv` key heads a value head). Without any of the three it is `prefill_masked`."""
+    key heads share value heads (`vdiv` key heads a value head). Without any of the three it is `prefill_masked`; the
+    tcgen05 kernel takes bfloat16 heads of 64 or 128 with keys and values of one width, the general kernel the rest."""
     if not softcap and not keep_first and vdiv == 1:
         prefill_masked(q, out, ctx, H, KV, HD, VD, k_cache, v_cache, pages, window, 0, scale)
+        return
+    if (USE_TC_MASKED and USE_TCGEN05_PREFILL and HD == VD and scale > 0.0
+            and kernels.attn_prefill_tcgen05_supported(q.dtype, H, KV, HD)):
+        kernels.attn_prefill_tcgen05_capped(q, out, ctx, H, KV, HD, k_cache, v_cache, pages, window, scale, softcap,
+                                            keep_first, vdiv)
         return
     kernels.attn_prefill_capped(q, out, ctx, H, KV, HD, VD, k_cache, v_cache, pages, window, scale, softcap, keep_first, vdiv)
 

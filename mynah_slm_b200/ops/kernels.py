@@ -1237,6 +1237,23 @@ def attn_prefill_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int
          int(keep_first or 0), int(vdiv), ptr(ctx.status), stream_ptr())
 
 
+def attn_prefill_tcgen05_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, k_cache: torch.Tensor,
+                                v_cache: torch.Tensor, pages: PageTableView, window: int, scale: float, softcap: float,
+                                keep_first: int, vdiv: int) -> None:
+    """The tcgen05 prompt attention with capped scores, first tokens that the window keeps (the page lists must hold
+    every page: a cache that gives pages back does not go with kept tokens) and `vdiv` key heads on one value head."""
+    for t, n in ((q, "q"), (out, "attention output")):
+        _rows(t, "attn_prefill_tcgen05: " + n)
+        if t.dtype != torch.bfloat16 or t.stride(0) % 8 or t.data_ptr() % 16:
+            raise KernelError(f"attn_prefill_tcgen05: {n} must be bfloat16 rows, 16-byte aligned")
+    _chk(k_cache, "K cache", torch.bfloat16)
+    _chk(v_cache, "V cache", torch.bfloat16)
+    call("mynah_attn_prefill_tcgen05_capped", ptr(q), ptr(out), q.shape[0], ctx.B, ctx.max_q_len, H, KV, HD, q.stride(0),
+         out.stride(0), ptr(k_cache), ptr(v_cache), ptr(ctx.cu_q), ptr(ctx.kv_len), ptr(pages.indptr), ptr(pages.ids),
+         ptr(pages.base), pages.n_pages, window or 0, 0, float(scale), float(softcap or 0.0), int(keep_first or 0), int(vdiv),
+         ptr(ctx.status), stream_ptr())
+
+
 def attn_decode_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, VD: int, k_cache, v_cache,
                        pages: PageTableView, window: int, scale: float, softcap: float, keep_first: int, vdiv: int,
                        scratch: torch.Tensor) -> None:

@@ -150,22 +150,34 @@ def capped_window_attention(h, W, p, m, eps, positions):
     return out.reshape(T, H * vd) @ W[p + "o"].T
 
 
-def pick_experts(h, W, p, router):
-    """(experts [T, top], weights [T, top]) in the order of the choice."""
+def pick_experts(h, W, p, router, margins=None):
+    """(experts [T, top], weights [T, top]) in the order of the choice. `margins`, a list, receives per token the
+    smallest gap by which a group or an expert made it into the choice (inf where nothing was left out)."""
     E, top = int(router["experts"]), int(router["top"])
     s = sigmoid(h @ W[p + "router"].T)
     choice = s + W[p + "correction"]
     groups = router.get("groups")
+    gap = np.full(h.shape[0], np.inf)
     if groups:
         n, keep = int(groups["count"]), int(groups["keep"])
         per = E // n
         g = choice.reshape(-1, n, per)
         score = np.sort(g, axis=-1)[..., -2:].sum(-1)                     # a group's two largest
         best = np.argsort(-score, axis=-1, kind="stable")[:, :keep]
+        if keep < n:
+            ordered = -np.sort(-score, axis=-1)
+            gap = np.minimum(gap, ordered[:, keep - 1] - ordered[:, keep])
         allowed = np.zeros((h.shape[0], n), dtype=bool)
         np.put_along_axis(allowed, best, True, axis=1)
         choice = np.where(np.repeat(allowed, per, axis=1), choice, -np.inf)
     picked = np.argsort(-choice, axis=-1, kind="stable")[:, :top]
+    if margins is not None:
+        ordered = -np.sort(-choice, axis=-1)
+        if top < E:
+            with np.errstate(invalid="ignore"):
+                d = ordered[:, top - 1] - ordered[:, top]
+            gap = np.minimum(gap, np.where(np.isnan(d), np.inf, d))
+        margins.append(gap)
     return picked, np.take_along_axis(s, picked, axis=1) * float(router["scale"])
 
 
@@ -175,8 +187,8 @@ def expert(h, W, p, limit):
     return (g * sigmoid(1.702 * g) * (u + 1.0)) @ W[p + "down"].T
 
 
-def grouped_moe(h, W, p, mlp):
-    picked, weights = pick_experts(h, W, p, mlp["router"])
+def grouped_moe(h, W, p, mlp, margins=None):
+    picked, weights = pick_experts(h, W, p, mlp["router"], margins)
     out = np.zeros((h.shape[0], W[p + "e0.down"].shape[0]))
     for t in range(h.shape[0]):
         for e, w in zip(picked[t], weights[t]):
@@ -201,8 +213,9 @@ def layer_runs(cfg):
     return runs + [(i, None) for i in range(stop, n)]
 
 
-def forward(cfg, W, tokens, layers_out=None):
-    """Logits [T, vocab] of one sequence from position 0; `layers_out`, a list, receives the stream behind every run."""
+def forward(cfg, W, tokens, layers_out=None, margins=None):
+    """Logits [T, vocab] of one sequence from position 0; `layers_out`, a list, receives the stream behind every run,
+    `margins`, a list, every routed feed-forward's per-token gap between chosen and not chosen (see pick_experts)."""
     tokens = np.asarray(tokens, dtype=np.int64)
     positions = np.arange(len(tokens))
     eps = float(cfg["norm"]["eps"])
@@ -215,7 +228,7 @@ def forward(cfg, W, tokens, layers_out=None):
         x = x + MIXERS[L["type"]](h, W, p + "mix.", L["mixer"], eps, positions)
         if L.get("mlp") is not None:
             h = rms_unit(x, eps) * W[p + "norm2"]
-            x = x + grouped_moe(h, W, p + "mlp.", L["mlp"])
+            x = x + grouped_moe(h, W, p + "mlp.", L["mlp"], margins)
         if layers_out is not None:
             layers_out.append(x.copy())
     return (rms_unit(x, eps) * W["final.norm"]) @ np.asarray(W["head"], dtype=np.float64).T
