@@ -8,6 +8,7 @@ and 64.
     python bench.py --design supisun      (the Supisun design beside Qwen3 at equal size, a JSON line of its own)
     python bench.py --design nedupel      (the Nedupel design beside Supisun and Qwen3 at equal size, likewise)
     python bench.py --design gupizen      (the Gupizen design beside Supisun, Nedupel and Qwen3 at equal size, likewise)
+    python bench.py --design gomuzen      (the Gomuzen design beside Nedupel, Supisun and Qwen3 at equal size, likewise)
 
 One JSON line on stdout. A step is one decode step of the batch.
   value     decoded tokens per second, timed on the device with CUDA events
@@ -360,6 +361,33 @@ def gupizen_config(shape: str, layers: int) -> dict:
             "canon": {"taps": 3}, "embedding": {"scale": D ** 0.5}, "layers": [pattern[i % 3] for i in range(layers)]}
 
 
+# The Gomuzen design at layer sizes that resemble a real model's, beside Nedupel (the closest existing design: latent
+# attention and clamped-gate experts), Supisun and Qwen3 at equal width, depth, heads and vocabulary. Its layers repeat
+# (latent attention with an output gate, differential attention, windowed attention, windowed attention): the latent
+# layers keep a cache row of 96 + 32 values; the differential layers have half the heads, each with two score maps of
+# the head size; the windowed layers see 1,024 positions and the first 4 tokens, with capped scores and interpolated
+# rotations; every layer has 16 experts in 4 groups (2 kept) of half the dense width of which a token uses 2.
+def gomuzen_config(shape: str, layers: int) -> dict:
+    c = dict(QWEN3_0_6B)
+    c.update(SHAPES[shape])
+    D, H, G, HD, F = c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"], c["intermediate_size"]
+    moe = {"kind": "moe", "expert": {"ff": F // 2, "limit": 7.0},
+           "router": {"experts": 16, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    yarn = {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}
+    lat = {"type": "latent_attention", "mlp": moe, "mixer": {
+        "heads": H, "dim": HD - 32, "rot_dim": 32, "vdim": HD, "kv_rank": 96, "scale": HD ** -0.5,
+        "rot": {"dims": 32, "base": 1e6, "scaling": yarn}}}
+    dif = {"type": "attention", "mlp": moe, "mixer": {
+        "heads": H // 2, "kv_heads": max(G // 2, 1), "dim": HD, "vdim": HD, "scale": HD ** -0.5, "softcap": 50.0, "diff": 0.6,
+        "rot": {"dims": HD // 2, "base": 1e6}}}
+    win = {"type": "attention_2", "mlp": moe, "mixer": {
+        "heads": H, "kv_heads": G, "dim": HD, "vdim": HD, "scale": HD ** -0.5, "softcap": 30.0,
+        "rot": {"dims": HD, "base": 1e6, "scaling": yarn}, "mask": {"size": 1024, "keep_first": 4}}}
+    pattern = [lat, dif, win, win]
+    return {"architecture": "Gomuzen", "vocab": c["vocab_size"], "width": D, "max_positions": 8192, "norm": {"eps": 1e-6},
+            "layers": [pattern[i % 4] for i in range(layers)]}
+
+
 def run_design(args) -> int:
     """`--design NAME`: prefill of one 2,048-token prompt and decode steps at --batch behind 2,048-token prompts, for
     the design and for the existing models at equal size (`--model` runs one of them: for a launch list of that model alone)."""
@@ -382,8 +410,10 @@ def run_design(args) -> int:
         q["num_hidden_layers"] = layers
         res = {"layers": layers}
         arms = [("supisun", supisun_config(shape, layers)), ("qwen3", q)]
-        if args.design in ("nedupel", "gupizen"):
+        if args.design in ("nedupel", "gupizen", "gomuzen"):
             arms.insert(0, ("nedupel", nedupel_config(shape, layers)))
+        if args.design == "gomuzen":
+            arms.insert(0, ("gomuzen", gomuzen_config(shape, layers)))
         if args.design == "gupizen":
             arms.insert(0, ("gupizen", gupizen_config(shape, layers)))
         for name, cfg in arms:
@@ -493,9 +523,9 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="prompt length of the decode phases")
     ap.add_argument("--shape", default="0.6b", choices=sorted(SHAPES), help="layer sizes, for --only runs (the full line is always 0.6b)")
     ap.add_argument("--workload", default="", choices=["", "4b", "8b"], help="run one of the two larger workloads instead")
-    ap.add_argument("--design", default="", choices=["", "supisun", "nedupel", "gupizen"],
+    ap.add_argument("--design", default="", choices=["", "supisun", "nedupel", "gupizen", "gomuzen"],
                     help="measure this design beside Qwen3 at equal size instead (prefill and decode; a line of its own)")
-    ap.add_argument("--model", default="", choices=["", "supisun", "nedupel", "gupizen", "qwen3"], help="with --design: only this one of the models")
+    ap.add_argument("--model", default="", choices=["", "supisun", "nedupel", "gupizen", "gomuzen", "qwen3"], help="with --design: only this one of the models")
     args = ap.parse_args()
 
     if args.impl == "reference":

@@ -63,7 +63,28 @@ struct TcArgs {
     int H, KV, ldq;
     int window, S;          // window: see first_visible
     float scale;
+    int keep_first = 0;     // with a window (> 0): keys at positions below it are seen whatever their distance; the page
+                            // lists must then hold every page of a sequence
+    int vdiv = 1;           // kv head g reads value head g / vdiv (the value cache has KV / vdiv heads)
+    float softcap = 0.f;    // c > 0: score <- c tanh(score / c), after the scale
 };
+
+// The pages that a sequence's newest position sees: pages [pg0, pg1) of its window (or of everything), and before them
+// `nf` pages that hold kept first tokens and lie wholly before the window.
+struct VisiblePages {
+    int lo, pg0, pg1, nf;
+    __device__ __forceinline__ int count() const { return nf + pg1 - pg0; }
+    __device__ __forceinline__ int page(int s) const { return s < nf ? s : (pg0 + s - nf < pg1 ? pg0 + s - nf : -1); }
+};
+__device__ __forceinline__ VisiblePages visible_pages(int hi, int window, int keep_first) {
+    VisiblePages v{0, 0, 0, 0};
+    if (hi <= 0) return v;
+    v.lo = first_visible(hi, window);
+    v.pg0 = v.lo / PAGE_TOKENS;
+    v.pg1 = (hi - 1) / PAGE_TOKENS + 1;
+    if (window > 0 && keep_first > 0) v.nf = min((keep_first + PAGE_TOKENS - 1) / PAGE_TOKENS, v.pg0);
+    return v;
+}
 
 // Byte offset of 16-byte chunk c of row r in a tile whose rows hold CH chunks:
 // the low three bits of the chunk index are xor-ed with the row, so the eight
@@ -94,6 +115,8 @@ struct PageJob {
     int s, g, b;                      // index among the sequence's visible pages, kv head, sequence
     int page;                         // physical page
     int k_first, k_last;              // rows of the tile in use
+    int h_first, h_last;              // rows among them that are not seen (between kept first tokens and the window); none: 1, 0
+    __device__ __forceinline__ bool sees(int r) const { return r >= k_first && r <= k_last && !(r >= h_first && r <= h_last); }
     size_t row0;                      // partial of head g*G+i: row0 + i*S
     bool empty;                       // nothing of this page is visible
 };
@@ -102,18 +125,30 @@ template <int HD>
 __device__ __forceinline__ PageJob page_job(int s, int g, int b, const int* __restrict__ kv_len, const PageTable& pt,
                                             const TcArgs& a, int* __restrict__ status, bool reporter) {
     PageJob j;
-    j.s = s; j.g = g; j.b = b; j.page = -1; j.k_first = 0; j.k_last = -1;
+    j.s = s; j.g = g; j.b = b; j.page = -1; j.k_first = 0; j.k_last = -1; j.h_first = 1; j.h_last = 0;
     const int G = a.H / a.KV;
     const int hi = kv_len[b];
-    const int lo = first_visible(hi, a.window);
+    const VisiblePages vp = visible_pages(hi, a.window, a.keep_first);
+    const int lo = vp.lo, kf = a.window > 0 ? a.keep_first : 0;
     int key_begin = 0, key_end = 0;
     if (hi > 0) {
-        const int pg0 = lo / PAGE_TOKENS, pg1 = (hi - 1) / PAGE_TOKENS + 1;
-        if (pg1 - pg0 > a.S && reporter && s == 0) atomicOr(status, MYNAH_ST_SPLIT_RANGE);
-        const int mp = pg0 + s;
-        if (mp < pg1) {
-            key_begin = max(lo, mp * PAGE_TOKENS);
-            key_end = min(hi, (mp + 1) * PAGE_TOKENS);
+        if (vp.count() > a.S && reporter && s == 0) atomicOr(status, MYNAH_ST_SPLIT_RANGE);
+        const int mp = vp.page(s);
+        if (mp >= 0) {
+            const int p0 = mp * PAGE_TOKENS, win0 = max(lo, p0);    // the page's first key, and its first key inside the window
+            key_end = min(hi, p0 + PAGE_TOKENS);
+            if (mp < vp.pg0) {                                      // a page of kept first tokens before the window
+                key_begin = p0;
+                key_end = min(key_end, kf);
+            } else if (kf > p0) {                                   // kept tokens and the window meet on this page
+                key_begin = p0;
+                if (kf < win0) {
+                    j.h_first = kf - p0;
+                    j.h_last = win0 - p0 - 1;
+                }
+            } else {
+                key_begin = win0;
+            }
             j.page = page_of(pt, b, mp * PAGE_TOKENS);
             if (j.page < 0) {
                 if (reporter) atomicOr(status, MYNAH_ST_PAGE_RANGE);
@@ -144,15 +179,15 @@ __device__ __forceinline__ void issue_page_copies(const PageJob& j, const bf16* 
                                                   const TcArgs& a, uint32_t k_base, uint32_t v_base) {
     constexpr int CH = HD / 8;
     const bf16* k_src = k_cache + ((size_t)j.page * a.KV + j.g) * PAGE_TOKENS * HD;
-    const bf16* v_src = v_cache + ((size_t)j.page * a.KV + j.g) * PAGE_TOKENS * HD;
+    const bf16* v_src = v_cache + ((size_t)j.page * (a.KV / a.vdiv) + j.g / a.vdiv) * PAGE_TOKENS * HD;
     for (int i = threadIdx.x; i < KEYS * CH; i += blockDim.x) {
         const int r = i / CH, c = i % CH;
-        cp_async_16(k_base + swz<CH>(r, c), k_src + (size_t)r * HD + c * 8, r >= j.k_first && r <= j.k_last);
+        cp_async_16(k_base + swz<CH>(r, c), k_src + (size_t)r * HD + c * 8, j.sees(r));
     }
     cp_async_commit();
     for (int i = threadIdx.x; i < KEYS * CH; i += blockDim.x) {
         const int r = i / CH, c = i % CH;
-        cp_async_16(v_base + swz<CH>(r, c), v_src + (size_t)r * HD + c * 8, r >= j.k_first && r <= j.k_last);
+        cp_async_16(v_base + swz<CH>(r, c), v_src + (size_t)r * HD + c * 8, j.sees(r));
     }
     cp_async_commit();
 }
@@ -209,8 +244,10 @@ __device__ __forceinline__ void compute_page_core(const PageJob& job, const uint
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int key = warp * 16 + t * 8 + (lane & 3) * 2 + (e & 1);
-            const bool vis = key >= k_first && key <= k_last;
-            sc[t][e] = vis ? sc[t][e] * a.scale : -INFINITY;
+            const bool vis = key >= k_first && key <= k_last && !(key >= job.h_first && key <= job.h_last);
+            float sv = sc[t][e] * a.scale;
+            if (a.softcap > 0.f) sv = a.softcap * tanhf(sv / a.softcap);
+            sc[t][e] = vis ? sv : -INFINITY;
             mx[e >> 1] = fmaxf(mx[e >> 1], sc[t][e]);
         }
 #pragma unroll
@@ -370,8 +407,7 @@ attn_decode_tc_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cac
         __syncthreads();
         if (!last_flag) return;
         const int hi = kv_len[b];
-        const int lo = first_visible(hi, a.window);
-        const int n_vis = hi > 0 ? min(a.S, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;
+        const int n_vis = min(a.S, visible_pages(hi, a.window, a.keep_first).count());
         merge_pages<HD>(part_o, part_ml, out + (size_t)b * ldo + (size_t)g * G * HD, ((size_t)b * a.H + (size_t)g * G) * a.S,
                         G, a.S, n_vis, reinterpret_cast<float*>(k_s), reinterpret_cast<float*>(v_s), red_m[0]);
     }
@@ -465,7 +501,7 @@ __device__ __forceinline__ void merge_pages(const float* __restrict__ part_o, co
 template <int HD>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
-                         const int* __restrict__ kv_len, int window, int H, int S, int ldo) {
+                         const int* __restrict__ kv_len, int window, int keep_first, int H, int S, int ldo) {
     constexpr int NS = WARPS * 32 / (HD / 4);
     extern __shared__ float w_s[];
     __shared__ __align__(16) float acc_s[NS * HD];
@@ -474,8 +510,7 @@ attn_decode_merge_kernel(const float* __restrict__ part_o, const float* __restri
     griddep_wait();
     griddep_launch_small();
     const int hi = kv_len[b];
-    const int lo = first_visible(hi, window);
-    const int n_vis = hi > 0 ? min(S, (hi - 1) / PAGE_TOKENS + 1 - lo / PAGE_TOKENS) : 0;
+    const int n_vis = min(S, visible_pages(hi, window, keep_first).count());
     merge_pages<HD>(part_o, part_ml, out + (size_t)b * ldo + (size_t)h * HD, ((size_t)b * H + h) * S, 1, S, n_vis, w_s, acc_s, inv_s);
 }
 
@@ -623,8 +658,8 @@ attn_decode_fused_kernel(const bf16* __restrict__ qkv, VecRef q_gain, VecRef k_g
         // the page's partial result: the same code as the pages' kernel (the probabilities go where the queries were)
         PageJob job;
         job.s = s; job.g = g; job.b = b; job.page = page;
-        job.k_first = k_first; job.k_last = k_last; job.row0 = row0; job.empty = false;
-        const TcArgs ta{a.H, a.KV, a.ldq, a.window, a.S, a.scale};
+        job.h_first = 1; job.h_last = 0; job.k_first = k_first; job.k_last = k_last; job.row0 = row0; job.empty = false;
+        const TcArgs ta{a.H, a.KV, a.ldq, a.window, a.S, a.scale, 0, 1, 0.f};
         compute_page<HD, 1, 0>(job, qa, ta, k_base, v_base, p_s, red_m, red_l, part_o, part_ml);
     }
 
@@ -777,7 +812,7 @@ attn_decode_stream_kernel(const __grid_constant__ CUtensorMap map_k, const __gri
         bool released = false;
         PageJob job;
         job.s = 0; job.g = sj.g; job.b = sj.b; job.page = 0;
-        job.k_first = sj.k_first; job.k_last = sj.k_last; job.row0 = (size_t)sj.row0; job.empty = sj.empty != 0;
+        job.h_first = 1; job.h_last = 0; job.k_first = sj.k_first; job.k_last = sj.k_last; job.row0 = (size_t)sj.row0; job.empty = sj.empty != 0;
         if (job.empty) {
             for (int i = tid; i < G; i += WARPS * 32) {
                 part_ml[(job.row0 + (size_t)i * a.S) * 2] = -INFINITY;
@@ -914,6 +949,13 @@ MYNAH_API int mynah_attn_decode_tc(
                                    n_pages, window, 0, 0.f, n_splits, scratch, counters, status, stream);
 }
 
+MYNAH_API int mynah_attn_decode_tc_capped(
+    const void* q, void* out, int B, int H, int KV, int HD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window_in, int chunk, float scale, float softcap, int keep_first, int vdiv, int n_splits, float* scratch,
+    unsigned* counters, int* status, cudaStream_t stream);
+
 // The same with a chunk mask instead of the window (one of the two, 0: none) and a score scale given by the caller
 // (0: 1/sqrt(HD)).
 MYNAH_API int mynah_attn_decode_tc_ex(
@@ -921,14 +963,29 @@ MYNAH_API int mynah_attn_decode_tc_ex(
     const void* k_cache, const void* v_cache, const int* kv_len,
     const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
     int window_in, int chunk, float scale, int n_splits, float* scratch, unsigned* counters, int* status, cudaStream_t stream) {
+    return mynah_attn_decode_tc_capped(q, out, B, H, KV, HD, ldq, ldo, k_cache, v_cache, kv_len, page_indptr, page_ids, page_base,
+                                       n_pages, window_in, chunk, scale, 0.f, 0, 1, n_splits, scratch, counters, status, stream);
+}
+
+// The same with capped scores (softcap c > 0: score <- c tanh(score / c), after the scale), first tokens that the window
+// keeps (keep_first, with a window and no chunk; the page lists must then hold every page of a sequence) and `vdiv` key
+// heads on one value head (the value cache is [n_pages, KV / vdiv, 64, HD]).
+MYNAH_API int mynah_attn_decode_tc_capped(
+    const void* q, void* out, int B, int H, int KV, int HD, int ldq, int ldo,
+    const void* k_cache, const void* v_cache, const int* kv_len,
+    const int* page_indptr, const int* page_ids, const int* page_base, int n_pages,
+    int window_in, int chunk, float scale, float softcap, int keep_first, int vdiv, int n_splits, float* scratch,
+    unsigned* counters, int* status, cudaStream_t stream) {
     if (B == 0) return 0;
     MYNAH_REQUIRE(window_in >= 0 && chunk >= 0 && !(window_in > 0 && chunk > 0), "attn_decode_tc: a window or a chunk, not both");
+    MYNAH_REQUIRE(softcap >= 0.f && keep_first >= 0 && vdiv >= 1 && KV % vdiv == 0 && (keep_first == 0 || chunk == 0),
+                  "attn_decode_tc: bad cap, kept tokens or value sharing");
     const int window = chunk > 0 ? -chunk : window_in;
     MYNAH_REQUIRE(mynah_attn_decode_tc_supported(H, KV, HD), "attn_decode_tc: H=%d KV=%d head_dim=%d is not taken by this kernel", H, KV, HD);
     MYNAH_REQUIRE(ldq % 8 == 0, "attn_decode_tc: query row stride %d must be a multiple of 8", ldq);
     MYNAH_REQUIRE(n_splits >= 1 && n_splits <= 65535 && B <= 65535 && KV <= 65535, "attn_decode_tc: launch too large");
     MYNAH_REQUIRE(scratch != nullptr, "attn_decode_tc: no scratch memory given");
-    const TcArgs a{H, KV, ldq, window, n_splits, scale != 0.f ? scale : 1.0f / sqrtf((float)HD)};
+    const TcArgs a{H, KV, ldq, window, n_splits, scale != 0.f ? scale : 1.0f / sqrtf((float)HD), window > 0 ? keep_first : 0, vdiv, softcap};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     float* part_o = scratch;
     float* part_ml = scratch + (size_t)B * H * n_splits * HD;
@@ -948,7 +1005,9 @@ MYNAH_API int mynah_attn_decode_tc_ex(
     // partial results are the same bits either way. Measured at the 0.6B shape: 64 sequences of 2,060 positions
     // 3.69 -> 3.63 ms a step, of 3,900 positions 6.03 -> 5.73; 16 sequences of 2,060 positions 1.74 -> 1.76 (so not there).
     const long long n_ctas = (long long)n_splits * KV * B;
-    const bool as_stream = stream_mode() != 0 && B <= STREAM_MAX_SEQS && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 &&
+    // (the stream form knows neither kept first tokens nor shared value heads: its jobs carry one range of rows a page and
+    // one tensor map's coordinates for keys and values alike)
+    const bool as_stream = a.keep_first == 0 && a.vdiv == 1 && stream_mode() != 0 && B <= STREAM_MAX_SEQS && ((uintptr_t)q & 15) == 0 && ((uintptr_t)k_cache & 15) == 0 &&
                            ((uintptr_t)v_cache & 15) == 0 && (stream_mode() == 2 || n_ctas >= (long long)mynah_sm_count() * 6 * 16);
     if (as_stream) {
         int rc;
@@ -971,9 +1030,9 @@ MYNAH_API int mynah_attn_decode_tc_ex(
     const size_t dyn = (size_t)n_splits * sizeof(float);
     MYNAH_REQUIRE(dyn <= MERGE_MAX_BYTES, "attn_decode_tc: %d pages a sequence exceed what the merge holds", n_splits);
     if (HD == 128)
-        mynah_launch(attn_decode_merge_kernel<128>, dim3(H, B), dim3(WARPS * 32), dyn, stream, part_o, part_ml, (bf16*)out, kv_len, window, H, n_splits, ldo);
+        mynah_launch(attn_decode_merge_kernel<128>, dim3(H, B), dim3(WARPS * 32), dyn, stream, part_o, part_ml, (bf16*)out, kv_len, window, a.keep_first, H, n_splits, ldo);
     else
-        mynah_launch(attn_decode_merge_kernel<64>, dim3(H, B), dim3(WARPS * 32), dyn, stream, part_o, part_ml, (bf16*)out, kv_len, window, H, n_splits, ldo);
+        mynah_launch(attn_decode_merge_kernel<64>, dim3(H, B), dim3(WARPS * 32), dyn, stream, part_o, part_ml, (bf16*)out, kv_len, window, a.keep_first, H, n_splits, ldo);
     return mynah_check_launch("attn_decode_merge");
 }
 
@@ -1015,9 +1074,9 @@ MYNAH_API int mynah_attn_decode_fused(
         if (mynah_check_launch("attn_decode_fused (pages)")) return -1;
         const size_t dyn_m = (size_t)n_splits * sizeof(float);
         if (HD == 128)
-            mynah_launch(attn_decode_merge_kernel<128>, dim3(H, B), dim3(WARPS * 32), dyn_m, stream, part_o, part_ml, (bf16*)out, kv_len, window, H, n_splits, ldo);
+            mynah_launch(attn_decode_merge_kernel<128>, dim3(H, B), dim3(WARPS * 32), dyn_m, stream, part_o, part_ml, (bf16*)out, kv_len, window, 0, H, n_splits, ldo);
         else
-            mynah_launch(attn_decode_merge_kernel<64>, dim3(H, B), dim3(WARPS * 32), dyn_m, stream, part_o, part_ml, (bf16*)out, kv_len, window, H, n_splits, ldo);
+            mynah_launch(attn_decode_merge_kernel<64>, dim3(H, B), dim3(WARPS * 32), dyn_m, stream, part_o, part_ml, (bf16*)out, kv_len, window, 0, H, n_splits, ldo);
         return mynah_check_launch("attn_decode_merge");
     }
     if (HD == 128)

@@ -51,7 +51,7 @@ struct PfArgs {
     int keep_first;                   // with a window: keys at positions below it are seen whatever their distance (every
                                       // page of the sequence must then be in the page list: nothing was given back)
     int vdiv;                         // kv head g reads value head g / vdiv (the value cache has KV / vdiv heads)
-    float cap_in, cap_log2;           // capped scores (CAP kernels): c tanh(s scale / c) log2(e) = cap_log2 * tanh(s * cap_in / 2)
+    float cap_in, cap_log2;           // capped scores (CAP kernels): c tanh(s scale / c) log2(e) = cap_log2 * tanh(s * cap_in)
     // The first key that the row at position p sees. Window and chunk both give a bound that does not fall as p
     // grows, so a tile's first row has the tile's lowest bound and its last row the highest.
     __device__ __forceinline__ bool bounded() const { return window > 0 || chunk > 0; }
@@ -118,9 +118,12 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 
 // NS: stages of K, V and the scores. 2: a CTA an SM, the next tile's scores and operands under this tile's softmax.
 // 1: half the shared and tensor memory, so that two CTAs share an SM and one's softmax runs under the other's products.
-// A score in the base-2 domain under a cap: cap_log2 * tanh(s * cap_in / 2), with tanh(x) = 1 - 2 / (e^(2x) + 1).
-__device__ __forceinline__ float capped_log2(float s, float cap_in, float cap_log2) {
-    return s == -INFINITY ? -INFINITY : cap_log2 * (1.0f - __fdividef(2.0f, ex2(s * cap_in) + 1.0f));
+// A score in the base-2 domain under a cap, less the row's reference: cap_log2 * tanh(s * cap_in) - m; -inf stays -inf.
+// The hardware's tanh has a relative error of 2^-11, a quarter of what the bfloat16 operands leave in a score.
+__device__ __forceinline__ float capped_log2(float s, float cap_in, float cap_log2, float m) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(s * cap_in));
+    return s == -INFINITY ? -INFINITY : fmaf(t, cap_log2, -m);
 }
 
 template <int HD, int NS, bool CAP>
@@ -389,7 +392,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!warp_wait(x_full + 8 * xst, xuse)) { ok = false; break; }
             STAMP(j, 4);
             const float mx_row = fmaxf(mx_own, xch[(xst * 2 + (grp ^ 1)) * BQ + row]);
-            const float m_new = CAP ? capped_log2(mx_row, a.cap_in, a.cap_log2) : mx_row * a.scale_log2;
+            const float m_new = CAP ? capped_log2(mx_row, a.cap_in, a.cap_log2, 0.f) : mx_row * a.scale_log2;
             // The reference maximum follows the true one lazily: while the row's maximum stays within 2^8 of it
             // nothing is rescaled (the probabilities just exceed one by up to that factor, which fp32 sums and
             // bf16 products carry without loss). Both threads of a row take the same decision.
@@ -422,8 +425,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int e = 0; e < HALF_KEYS; e += 2) {
                     float x0, x1;
                     if constexpr (CAP) {
-                        x0 = capped_log2(s[e], a.cap_in, a.cap_log2) - m_use;
-                        x1 = capped_log2(s[e + 1], a.cap_in, a.cap_log2) - m_use;
+                        x0 = capped_log2(s[e], a.cap_in, a.cap_log2, m_use);
+                        x1 = capped_log2(s[e + 1], a.cap_in, a.cap_log2, m_use);
                     } else {
                         fma2(x0, x1, s[e], s[e + 1], a.scale_log2, -m_use);
                     }
@@ -446,8 +449,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     for (int e = 0; e < 32; e += 2) {
                         float x0, x1;
                         if constexpr (CAP) {
-                            x0 = capped_log2(v[e], a.cap_in, a.cap_log2) - m_use;
-                            x1 = capped_log2(v[e + 1], a.cap_in, a.cap_log2) - m_use;
+                            x0 = capped_log2(v[e], a.cap_in, a.cap_log2, m_use);
+                            x1 = capped_log2(v[e + 1], a.cap_in, a.cap_log2, m_use);
                         } else {
                             fma2(x0, x1, v[e], v[e + 1], a.scale_log2, -m_use);
                         }
@@ -633,7 +636,7 @@ MYNAH_API int mynah_attn_prefill_tcgen05_capped(
     if (make_map(&mv, v_cache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)n_pages * (KV / vdiv) * PAGE_TOKENS, HD, HD, PAGE_TOKENS, 64)) return -1;
     const float scale_used = scale != 0.f ? scale : 1.0f / sqrtf((float)HD);
     const PfArgs a{B, H, KV, ldo, window, scale_used * 1.4426950408889634f, chunk, keep_first, vdiv,
-                   softcap > 0.f ? 2.0f * scale_used * 1.4426950408889634f / softcap : 0.f, softcap * 1.4426950408889634f};
+                   softcap > 0.f ? scale_used / softcap : 0.f, softcap * 1.4426950408889634f};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     // Two CTAs an SM pay once there are several waves of CTAs (64 prompts of 2,048 tokens and 32 heads: 2.97 against
     // 3.34 ms; 4 prompts: 221 against 236 us); with one wave or two, the longest CTA's own chain sets the time and it

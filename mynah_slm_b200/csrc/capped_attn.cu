@@ -64,8 +64,8 @@ capped_attn_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const 
     const T* row = qkv + (size_t)t * a.ld;
     const int n_units = a.Hq + (writes ? a.Gk + a.Gv : 0);
     float* mine = unit[warp];
-    for (int u = warp; u < n_units; u += PREP_WARPS) {
-        __syncwarp();
+    // a warp a unit: blockIdx.y numbers the groups of PREP_WARPS units of the token
+    for (int u = blockIdx.y * PREP_WARPS + warp; u < n_units; u = n_units) {
         if (u >= a.Hq + a.Gk) {                            // a value head: bias, then the cache
             const int g = u - a.Hq - a.Gk;
             const int col = (a.Hq + a.Gk) * a.dim + g * a.vd;
@@ -161,17 +161,27 @@ diff_combine_kernel(const T* __restrict__ a_in, T* __restrict__ out, const int* 
     }
 }
 
-template <typename T>
+// VEC values a thread (8: heads and row strides that are multiples of 8, 16-byte accesses; else 1)
+template <typename T, int VEC>
 __global__ void head_gate_kernel(T* __restrict__ x, int ldx, const T* __restrict__ gate, int ldg, int H, int vd, long long n) {
     griddep_launch_small();
     griddep_wait();
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
     if (i >= n) return;
     const int per = H * vd;
     const int t = (int)(i / per), c = (int)(i % per);
     const float z = to_f32(gate[(size_t)t * ldg + c / vd]);
+    const float g = 1.0f / (1.0f + expf(-z));
     T* p = x + (size_t)t * ldx + c;
-    *p = from_f32<T>(to_f32(*p) * (1.0f / (1.0f + expf(-z))));
+    if constexpr (VEC == 8) {
+        float v[8];
+        load8(p, v);
+#pragma unroll
+        for (int k = 0; k < 8; k++) v[k] *= g;
+        store8(p, v);
+    } else {
+        *p = from_f32<T>(to_f32(*p) * g);
+    }
 }
 
 }  // namespace
@@ -197,11 +207,14 @@ MYNAH_API int mynah_capped_attn_prep(const void* qkv, int dtype, int T, int ld, 
                            q_gain != nullptr ? 1 : 0, eps};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     const VecRef qg{q_gain, gain_dtype}, kg{k_gain, gain_dtype};
+    const int n_units = Hq + (k_cache != nullptr ? Gk + Gv : 0);
+    MYNAH_REQUIRE(ceil_div(n_units, PREP_WARPS) <= 65535, "capped_attn_prep: too many heads for one launch");
+    const dim3 grid(T, ceil_div(n_units, PREP_WARPS));
     if (dtype == MYNAH_F32)
-        mynah_launch(capped_attn_prep_kernel<float>, dim3(T), dim3(PREP_WARPS * 32), 0, stream, (const float*)qkv, (float*)q_out, bias,
+        mynah_launch(capped_attn_prep_kernel<float>, grid, dim3(PREP_WARPS * 32), 0, stream, (const float*)qkv, (float*)q_out, bias,
                      qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (float*)k_cache, (float*)v_cache, a, status);
     else if (dtype == MYNAH_BF16)
-        mynah_launch(capped_attn_prep_kernel<bf16>, dim3(T), dim3(PREP_WARPS * 32), 0, stream, (const bf16*)qkv, (bf16*)q_out, bias, qg,
+        mynah_launch(capped_attn_prep_kernel<bf16>, grid, dim3(PREP_WARPS * 32), 0, stream, (const bf16*)qkv, (bf16*)q_out, bias, qg,
                      kg, cos_t, sin_t, tok_seq, tok_pos, pt, (bf16*)k_cache, (bf16*)v_cache, a, status);
     else
         return mynah_fail("capped_attn_prep: unsupported dtype %d", dtype);
@@ -230,11 +243,16 @@ MYNAH_API int mynah_head_gate(void* x, int dtype, int T, int ldx, const void* ga
     if (T == 0) return 0;
     MYNAH_REQUIRE(T > 0 && H > 0 && vd > 0, "head_gate: bad sizes");
     const long long n = (long long)T * H * vd;
-    const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (dtype == MYNAH_F32)
-        mynah_launch(head_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, ldx, (const float*)gate, ldg, H, vd, n);
+    const bool vec = vd % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 31) == 0;
+    const unsigned blocks = (unsigned)((n / (vec ? 8 : 1) + 255) / 256);
+    if (dtype == MYNAH_F32 && vec)
+        mynah_launch(head_gate_kernel<float, 8>, dim3(blocks), dim3(256), 0, stream, (float*)x, ldx, (const float*)gate, ldg, H, vd, n);
+    else if (dtype == MYNAH_F32)
+        mynah_launch(head_gate_kernel<float, 1>, dim3(blocks), dim3(256), 0, stream, (float*)x, ldx, (const float*)gate, ldg, H, vd, n);
+    else if (dtype == MYNAH_BF16 && vec)
+        mynah_launch(head_gate_kernel<bf16, 8>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, ldx, (const bf16*)gate, ldg, H, vd, n);
     else if (dtype == MYNAH_BF16)
-        mynah_launch(head_gate_kernel<bf16>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, ldx, (const bf16*)gate, ldg, H, vd, n);
+        mynah_launch(head_gate_kernel<bf16, 1>, dim3(blocks), dim3(256), 0, stream, (bf16*)x, ldx, (const bf16*)gate, ldg, H, vd, n);
     else
         return mynah_fail("head_gate: unsupported dtype %d", dtype);
     return mynah_check_launch("head_gate");

@@ -132,5 +132,10 @@ def decode_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: 
     if not softcap and not keep_first and vdiv == 1:
         decode_masked(q, out, ctx, H, KV, HD, VD, k_cache, v_cache, pages, window, 0, scale, scratch)
         return
+    if (USE_TC_MASKED and HD == VD and scale > 0.0 and kernels.attn_decode_tc_supported(q.dtype, H, KV, HD)
+            and _tc_fits(H, KV, ctx.decode_splits)):
+        kernels.attn_decode_tc_capped(q, out, ctx, H, KV, HD, k_cache, v_cache, pages, window, scale, softcap, keep_first,
+                                      vdiv, scratch)
+        return
     kernels.attn_decode_capped(q, out, ctx, H, KV, HD, VD, k_cache, v_cache, pages, window, scale, softcap, keep_first, vdiv,
                                scratch)

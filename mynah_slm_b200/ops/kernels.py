@@ -1254,6 +1254,26 @@ def attn_prefill_tcgen05_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int,
          ptr(ctx.status), stream_ptr())
 
 
+def attn_decode_tc_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, k_cache: torch.Tensor,
+                          v_cache: torch.Tensor, pages: PageTableView, window: int, scale: float, softcap: float,
+                          keep_first: int, vdiv: int, scratch: torch.Tensor) -> None:
+    """The tensor-core decode attention with capped scores, first tokens that the window keeps (the page lists must hold
+    every page) and `vdiv` key heads on one value head."""
+    for t, n in ((q, "q"), (out, "attention output")):
+        _rows(t, "attn_decode_tc: " + n)
+        if t.dtype != torch.bfloat16 or t.stride(0) % 8 or t.data_ptr() % 16:
+            raise KernelError(f"attn_decode_tc: {n} must be bfloat16 rows, 16-byte aligned")
+    _chk(scratch, "scratch", torch.float32)
+    need = ctx.B * H * ctx.decode_splits * (HD + 2)
+    if scratch.numel() < need:
+        raise KernelError(f"attn_decode_tc: scratch holds {scratch.numel()} floats, {need} are needed")
+    call("mynah_attn_decode_tc_capped", ptr(q), ptr(out), ctx.B, H, KV, HD, q.stride(0), out.stride(0),
+         ptr(k_cache), ptr(v_cache), ptr(ctx.kv_len), ptr(pages.indptr), ptr(pages.ids), ptr(pages.base), pages.n_pages,
+         window or 0, 0, float(scale), float(softcap or 0.0), int(keep_first or 0), int(vdiv), ctx.decode_splits,
+         ptr(scratch), None, ptr(ctx.status), stream_ptr())
+    lib.add_launches(1)        # pages and their merge
+
+
 def attn_decode_capped(q: torch.Tensor, out: torch.Tensor, ctx, H: int, KV: int, HD: int, VD: int, k_cache, v_cache,
                        pages: PageTableView, window: int, scale: float, softcap: float, keep_first: int, vdiv: int,
                        scratch: torch.Tensor) -> None:

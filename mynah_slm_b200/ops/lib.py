@@ -130,6 +130,8 @@ _SIGNATURES: dict[str, list] = {
     "mynah_retention_scan": [P, P, P, c_int, c_int, c_int, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P],
     "mynah_attn_prefill_tcgen05_capped": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                           P, P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_float, c_int, c_int, P, P],
+    "mynah_attn_decode_tc_capped": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P, P, P, P, P, c_int,
+                                    c_int, c_int, c_float, c_float, c_int, c_int, c_int, P, P, P, P],
     "mynah_attn_prefill_generic_capped": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                           P, P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_float, c_int, c_int, P, P],
     "mynah_attn_decode_capped": [P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
