@@ -141,10 +141,10 @@ def run_attention(dtype, H, KV, vdiv, d, vd, q_lens, starts, scale, cap, window,
     k = [rnd(s + n, KV, d) for n, s in zip(q_lens, starts)]
     v = [rnd(s + n, KV // vdiv, vd) for n, s in zip(q_lens, starts)]
     if sharp is not None:                     # every query looks along e_0; the key at `sharp` of sequence 0 lies there
-        q[..., 0] = 8.0
+        q[..., 0] = 12.0
         for kb in k:
             kb[..., 0] = 0.0
-        k[0][sharp, :, 0] = 8.0
+        k[0][sharp, :, 0] = 12.0
     k_cache = torch.zeros((n_pages, KV, PAGE, d), dtype=dtype, device=DEV)
     v_cache = torch.zeros((n_pages, KV // vdiv, PAGE, vd), dtype=dtype, device=DEV)
     for b in range(len(q_lens)):
@@ -204,7 +204,7 @@ def test_one_key_stands_out_at_every_edge(dtype, d):
     tol = 1e-4 if dtype == torch.float32 else 3e-2
     for key in (0, 63, 64, 65, 66, 67, 127, 128, 200, 256, 257):
         for q_lens, starts in (([n], [0]), ([n - 250], [250])) + tuple(([1], [p]) for p in (key, key + 1, key + 71, key + 72, 300, 329) if key <= p < n):
-            ref, got, v = run_attention(dtype, 2, 2, 1, d, d, q_lens, starts, 1.0, 100.0, window, keep, key, sharp=key)
+            ref, got, v = run_attention(dtype, 2, 2, 1, d, d, q_lens, starts, 1.0, 200.0, window, keep, key, sharp=key)
             assert rel(ref, got) < tol, (key, q_lens, starts)
             for r, p in enumerate(range(starts[0], starts[0] + q_lens[0])):
                 sees = key <= p and (p - key < window or key < keep)
