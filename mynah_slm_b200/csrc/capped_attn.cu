@@ -124,6 +124,123 @@ capped_attn_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const 
     }
 }
 
+// The same for units that move 16 bytes at a time: `dim` a power of two from 8 to 256 and `vd` a multiple of 8 (no padding
+// columns), rotated pairs that lie whole chunks apart (rot a multiple of 16) or side by side (interleaved). A unit lies
+// across dim / 8 lanes, eight values a lane; a warp takes 256 / dim units at once; the partner of a rotated value is the
+// same register of another lane of the unit. grid (tokens, groups of units); the last group's CTA also copies the values.
+template <typename T>
+__global__ void __launch_bounds__(PREP_WARPS * 32)
+capped_attn_prep_vec_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const float* __restrict__ bias, VecRef q_gain,
+                            VecRef k_gain, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                            const int* __restrict__ tok_seq, const int* __restrict__ tok_pos, PageTable pt,
+                            T* __restrict__ k_cache, T* __restrict__ v_cache, CappedPrepArgs a, int* __restrict__ status) {
+    griddep_launch_small();
+    griddep_wait();
+    const int t = blockIdx.x;
+    const int b = tok_seq[t];
+    if (b < 0) return;                                    // a padding row
+    const int pos = tok_pos[t];
+    const bool rotate = a.rot > 0 && cos_t != nullptr;
+    if (rotate && (pos < 0 || pos >= a.n_pos)) {
+        if (threadIdx.x == 0) atomicOr(status, MYNAH_ST_POS_RANGE);
+        return;
+    }
+    const bool writes = k_cache != nullptr;
+    int page = -1;
+    if (writes) {
+        page = page_of(pt, b, pos);
+        if (page < 0) {
+            if (threadIdx.x == 0) atomicOr(status, MYNAH_ST_PAGE_RANGE);
+            return;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int L = a.dim >> 3, per_warp = 32 / L;           // lanes a unit, units a warp
+    const int half = a.rot >> 1;
+    const T* row = qkv + (size_t)t * a.ld;
+    const int n_qk = a.Hq + (writes ? a.Gk : 0);
+    if (writes && blockIdx.y == gridDim.y - 1) {           // the values: bias, then the cache
+        const int col0 = (a.Hq + a.Gk) * a.dim, chunks = a.Gv * a.vd / 8, cpv = a.vd / 8;
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+            float v[8];
+            load8(row + col0 + c * 8, v);
+            if (bias != nullptr) {
+#pragma unroll
+                for (int j = 0; j < 8; j++) v[j] += bias[col0 + c * 8 + j];
+            }
+            const int g = c / cpv;
+            store8(v_cache + (((size_t)page * a.Gv + g) * PAGE_TOKENS + pos % PAGE_TOKENS) * a.vd + (c % cpv) * 8, v);
+        }
+    }
+    const int u = (blockIdx.y * PREP_WARPS + warp) * per_warp + lane / L;
+    const int l = lane % L;
+    const bool on = u < n_qk;
+    const bool is_q = u < a.Hq;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (on) {
+        load8(row + (size_t)u * a.dim + l * 8, v);
+        if (bias != nullptr) {
+            float bv[8];
+            load8(bias + u * a.dim + l * 8, bv);
+#pragma unroll
+            for (int j = 0; j < 8; j++) v[j] += bv[j];
+        }
+    }
+    if (a.has_norm) {                                       // every lane takes part in the shuffles, units that are off too
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; j++) ss = fmaf(v[j], v[j], ss);
+        for (int o = L >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float s = 1.0f / sqrtf(ss / (float)a.dim + a.eps);
+        const VecRef& gain = is_q ? q_gain : k_gain;
+        float gv[8];
+        if (gain.dtype == MYNAH_F32) load8(static_cast<const float*>(gain.p) + l * 8, gv);
+        else load8(static_cast<const bf16*>(gain.p) + l * 8, gv);
+#pragma unroll
+        for (int j = 0; j < 8; j++) v[j] = (v[j] * s) * gv[j];
+    }
+    if (rotate) {
+        const float* cr = cos_t + (size_t)pos * half;
+        const float* sr = sin_t + (size_t)pos * half;
+        if (a.interleaved) {
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                if (l * 8 + j < a.rot) {                    // pairs beyond the rotated dimensions pass
+                    const int i = (l * 8 + j) >> 1;
+                    const float c = cr[i], sn = sr[i], x = v[j], y = v[j + 1];
+                    v[j] = x * c - y * sn;
+                    v[j + 1] = y * c + x * sn;
+                }
+            }
+        } else {
+            const int hl = half >> 3;                       // lanes between a value and its partner
+            const bool low = l < hl, in = l < 2 * hl;
+            const int src = (lane - l) + (in ? (low ? l + hl : l - hl) : l);
+            const int i0 = (low ? l : l - hl) * 8;
+            float cv[8] = {}, sv[8] = {};
+            if (in) {
+                load8(cr + i0, cv);
+                load8(sr + i0, sv);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float other = __shfl_sync(0xffffffffu, v[j], src);
+                if (in) v[j] = v[j] * cv[j] + (low ? -other : other) * sv[j];
+            }
+        }
+    }
+    if (!on) return;
+    T* dst;
+    if (is_q) {
+        const int h = u / a.maps, m = u % a.maps;
+        const int slot = ((h / a.R) * a.maps + m) * a.R + h % a.R;
+        dst = q_out + (size_t)t * a.ldq + (size_t)slot * a.dim;
+    } else {
+        dst = k_cache + (((size_t)page * a.Gk + (u - a.Hq)) * PAGE_TOKENS + pos % PAGE_TOKENS) * a.dim;
+    }
+    store8(dst + l * 8, v);
+}
+
 struct DiffArgs {
     int H, R, vd, vdp, lda, ldo;
     float lambda, mult, eps;
@@ -207,6 +324,27 @@ MYNAH_API int mynah_capped_attn_prep(const void* qkv, int dtype, int T, int ld, 
                            q_gain != nullptr ? 1 : 0, eps};
     const PageTable pt{page_indptr, page_ids, page_base, n_pages};
     const VecRef qg{q_gain, gain_dtype}, kg{k_gain, gain_dtype};
+    // units that move 16 bytes at a time take the vector form
+    const bool pow2 = (dim & (dim - 1)) == 0;
+    const bool vec = pow2 && dim >= 8 && dim <= 256 && vd % 8 == 0 && dimp == dim && vdp == vd && ld % 8 == 0 && ldq % 8 == 0 &&
+                     (cos_t == nullptr || rot == 0 || interleaved || rot % 16 == 0) &&
+                     (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & (dtype == MYNAH_F32 ? 31 : 15)) == 0 &&
+                     (((uintptr_t)bias | (uintptr_t)q_gain | (uintptr_t)k_gain | (uintptr_t)cos_t | (uintptr_t)sin_t) & 31) == 0;
+    if (vec) {
+        const int per_cta = PREP_WARPS * (256 / dim);
+        const int n_qk = Hq + (k_cache != nullptr ? Gk : 0);
+        MYNAH_REQUIRE(ceil_div(n_qk, per_cta) <= 65535, "capped_attn_prep: too many heads for one launch");
+        const dim3 vgrid(T, ceil_div(n_qk, per_cta));
+        if (dtype == MYNAH_F32)
+            mynah_launch(capped_attn_prep_vec_kernel<float>, vgrid, dim3(PREP_WARPS * 32), 0, stream, (const float*)qkv, (float*)q_out, bias,
+                         qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (float*)k_cache, (float*)v_cache, a, status);
+        else if (dtype == MYNAH_BF16)
+            mynah_launch(capped_attn_prep_vec_kernel<bf16>, vgrid, dim3(PREP_WARPS * 32), 0, stream, (const bf16*)qkv, (bf16*)q_out, bias,
+                         qg, kg, cos_t, sin_t, tok_seq, tok_pos, pt, (bf16*)k_cache, (bf16*)v_cache, a, status);
+        else
+            return mynah_fail("capped_attn_prep: unsupported dtype %d", dtype);
+        return mynah_check_launch("capped_attn_prep");
+    }
     const int n_units = Hq + (k_cache != nullptr ? Gk + Gv : 0);
     MYNAH_REQUIRE(ceil_div(n_units, PREP_WARPS) <= 65535, "capped_attn_prep: too many heads for one launch");
     const dim3 grid(T, ceil_div(n_units, PREP_WARPS));

@@ -62,7 +62,11 @@ def place(cache, pages_ids, indptr, b, rows):
 # ------------------------------------------------------------------ preparation
 @pytest.mark.parametrize("H,G,M,dim,vd,rot,interleaved,norm,bias", [
     (4, 2, 2, 16, 24, 8, False, True, False), (6, 2, 1, 16, 8, 16, False, False, True), (1, 1, 2, 10, 6, 6, False, True, True),
-    (3, 1, 1, 10, 7, 4, True, False, False), (5, 5, 2, 5, 9, 0, False, True, False)])
+    (3, 1, 1, 10, 7, 4, True, False, False), (5, 5, 2, 5, 9, 0, False, True, False),
+    # units that move 16 bytes at a time (the vector form): whole and partial rotations in both pairings, every width
+    (4, 2, 2, 64, 64, 32, False, True, False), (2, 1, 1, 128, 128, 128, False, False, True), (3, 3, 1, 32, 8, 32, True, True, True),
+    (2, 2, 2, 256, 40, 64, False, True, False), (8, 4, 1, 8, 8, 0, False, True, True), (6, 3, 1, 16, 24, 6, True, False, True),
+    (16, 8, 1, 128, 128, 64, False, True, True)])
 def test_capped_prep_and_cache_rows(H, G, M, dim, vd, rot, interleaved, norm, bias):
     from mynah_slm_b200.ops import kernels
     from mynah_slm_b200.parts.position import rotary_frequencies
