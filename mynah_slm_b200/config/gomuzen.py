@@ -119,9 +119,7 @@ class GomuzenConfig:
             if kind == "latent_attention":
                 for k in ("heads", "vdim", "kv_rank", "dim", "rot_dim"):
                     req_int(m, k)
-                _check_rot(m.get("rot"), m["rot_dim"], wm)
-                if m["rot"]["dims"] != m["rot_dim"]:
-                    raise ConfigError(f"{wm}: rot.dims {m['rot']['dims']} differs from rot_dim {m['rot_dim']}")
+                _check_rot(m.get("rot"), m["rot_dim"], wm)          # the rotated part's first rot.dims dimensions turn
             else:
                 for k in ("heads", "kv_heads", "dim", "vdim"):
                     req_int(m, k)

@@ -65,62 +65,62 @@ capped_attn_prep_kernel(const T* __restrict__ qkv, T* __restrict__ q_out, const 
     const int n_units = a.Hq + (writes ? a.Gk + a.Gv : 0);
     float* mine = unit[warp];
     // a warp a unit: blockIdx.y numbers the groups of PREP_WARPS units of the token
-    for (int u = blockIdx.y * PREP_WARPS + warp; u < n_units; u = n_units) {
-        if (u >= a.Hq + a.Gk) {                            // a value head: bias, then the cache
-            const int g = u - a.Hq - a.Gk;
-            const int col = (a.Hq + a.Gk) * a.dim + g * a.vd;
-            T* dst = v_cache + (((size_t)page * a.Gv + g) * PAGE_TOKENS + pos % PAGE_TOKENS) * a.vdp;
-            for (int d = lane; d < a.vdp; d += 32) {
-                float v = 0.f;
-                if (d < a.vd) v = to_f32(row[col + d]) + (bias != nullptr ? bias[col + d] : 0.f);
-                dst[d] = from_f32<T>(v);
-            }
-            continue;
-        }
-        const bool is_q = u < a.Hq;
-        const int col = u * a.dim;                         // q units, then k units, side by side
-        float ss = 0.f;
-        for (int d = lane; d < a.dim; d += 32) {
-            const float v = to_f32(row[col + d]) + (bias != nullptr ? bias[col + d] : 0.f);
-            mine[d] = v;
-            ss = fmaf(v, v, ss);
-        }
-        if (a.has_norm) {
-            ss = warp_sum(ss);
-            const float s = 1.0f / sqrtf(ss / (float)a.dim + a.eps);
-            const VecRef& gain = is_q ? q_gain : k_gain;
-            for (int d = lane; d < a.dim; d += 32) mine[d] = (mine[d] * s) * gain.at(d);
-        }
-        __syncwarp();
-        T* dst;
-        if (is_q) {
-            const int h = u / a.maps, m = u % a.maps;
-            const int slot = ((h / a.R) * a.maps + m) * a.R + h % a.R;
-            dst = q_out + (size_t)t * a.ldq + (size_t)slot * a.dimp;
-        } else {
-            dst = k_cache + (((size_t)page * a.Gk + (u - a.Hq)) * PAGE_TOKENS + pos % PAGE_TOKENS) * a.dimp;
-        }
-        for (int d = lane; d < a.dimp; d += 32) {
+    const int u = blockIdx.y * PREP_WARPS + warp;
+    if (u >= n_units) return;
+    if (u >= a.Hq + a.Gk) {                                // a value head: bias, then the cache
+        const int g = u - a.Hq - a.Gk;
+        const int col = (a.Hq + a.Gk) * a.dim + g * a.vd;
+        T* dst = v_cache + (((size_t)page * a.Gv + g) * PAGE_TOKENS + pos % PAGE_TOKENS) * a.vdp;
+        for (int d = lane; d < a.vdp; d += 32) {
             float v = 0.f;
-            if (d < a.dim) {
-                v = mine[d];
-                if (rotate && d < a.rot) {
-                    int i, other;
-                    float sign;
-                    if (a.interleaved) {
-                        i = d >> 1;
-                        other = d ^ 1;
-                        sign = (d & 1) ? 1.f : -1.f;
-                    } else {
-                        i = d < half ? d : d - half;
-                        other = d < half ? d + half : d - half;
-                        sign = d < half ? -1.f : 1.f;
-                    }
-                    v = v * cr[i] + sign * mine[other] * sr[i];
-                }
-            }
+            if (d < a.vd) v = to_f32(row[col + d]) + (bias != nullptr ? bias[col + d] : 0.f);
             dst[d] = from_f32<T>(v);
         }
+        return;
+    }
+    const bool is_q = u < a.Hq;
+    const int col = u * a.dim;                             // q units, then k units, side by side
+    float ss = 0.f;
+    for (int d = lane; d < a.dim; d += 32) {
+        const float v = to_f32(row[col + d]) + (bias != nullptr ? bias[col + d] : 0.f);
+        mine[d] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (a.has_norm) {
+        ss = warp_sum(ss);
+        const float s = 1.0f / sqrtf(ss / (float)a.dim + a.eps);
+        const VecRef& gain = is_q ? q_gain : k_gain;
+        for (int d = lane; d < a.dim; d += 32) mine[d] = (mine[d] * s) * gain.at(d);
+    }
+    __syncwarp();
+    T* dst;
+    if (is_q) {
+        const int h = u / a.maps, m = u % a.maps;
+        const int slot = ((h / a.R) * a.maps + m) * a.R + h % a.R;
+        dst = q_out + (size_t)t * a.ldq + (size_t)slot * a.dimp;
+    } else {
+        dst = k_cache + (((size_t)page * a.Gk + (u - a.Hq)) * PAGE_TOKENS + pos % PAGE_TOKENS) * a.dimp;
+    }
+    for (int d = lane; d < a.dimp; d += 32) {
+        float v = 0.f;
+        if (d < a.dim) {
+            v = mine[d];
+            if (rotate && d < a.rot) {
+                int i, other;
+                float sign;
+                if (a.interleaved) {
+                    i = d >> 1;
+                    other = d ^ 1;
+                    sign = (d & 1) ? 1.f : -1.f;
+                } else {
+                    i = d < half ? d : d - half;
+                    other = d < half ? d + half : d - half;
+                    sign = d < half ? -1.f : 1.f;
+                }
+                v = v * cr[i] + sign * mine[other] * sr[i];
+            }
+        }
+        dst[d] = from_f32<T>(v);
     }
 }
 

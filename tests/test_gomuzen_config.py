@@ -71,7 +71,7 @@ def _broken(path, value, base=gm.HYBRID):
 @pytest.mark.parametrize("path,value,word", [
     (("layers", 0, "type"), "mamba", "type"), (("layers", 1, "mixer", "softcap"), None, "softcap"),
     (("layers", 1, "mixer", "diff"), None, "diff"), (("layers", 1, "mixer", "kv_heads"), 3, "kv_heads"),
-    (("layers", 0, "mixer", "rot", "dims"), 6, "rot_dim"), (("layers", 2, "mixer", "rot", "dims"), 18, "rot.dims"),
+    (("layers", 0, "mixer", "rot", "dims"), 10, "rot.dims"), (("layers", 2, "mixer", "rot", "dims"), 18, "rot.dims"),
     (("layers", 2, "mixer", "mask", "size"), None, "size"), (("layers", 0, "mlp", "router", "groups", "count"), 4, "groups"),
     (("layers", 0, "mlp", "router", "top"), 5, "top"), (("layers", 0, "mlp", "router", "scale"), None, "scale"),
     (("layers", 0, "mlp", "expert", "limit"), None, "limit"), (("loop", "stop"), 9, "loop"), (("norm",), None, "norm"),
