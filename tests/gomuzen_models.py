@@ -75,7 +75,7 @@ PLAIN = config(48, 200, [
     moe(windowed(4, 2, 8, 8, 0.3, 20.0, 8, window=33, keep_first=3), 24, 1.5, 4, 2, 2.5, groups=(2, 1)),
     bare(latent(2, 8, 8, 8, 16, 0.25, base=300.0)),
 ])
-ONLY_LATENT = config(48, 200, [bare(latent(4, 16, 8, 8, 24, 0.25, base=300.0, scaling=(8.0, 32, 8.0, 2.0)))])
+ONLY_LATENT = config(48, 200, [bare(latent(4, 16, 8, 8, 24, 0.25, base=300.0, scaling=(8.0, 32, 8.0, 2.0)))], loop=(0, 1, 2))      # the one layer twice
 ONLY_DIFF = config(48, 200, [bare(differential(4, 2, 16, 12, 0.25, 12.0, 0.4, 12, base=1000.0))])
 ONLY_WINDOW = config(48, 200, [bare(windowed(4, 2, 16, 12, 0.25, 12.0, 16, base=1000.0, scaling=(8.0, 32, 8.0, 2.0), window=50, keep_first=7))])
 ONLY_SLIDE = config(48, 200, [bare(windowed(4, 2, 16, 12, 0.25, 12.0, 16, base=1000.0, window=70))])      # nothing kept: pages go back

@@ -426,3 +426,14 @@ def test_trace_runner_process(models, tmp_path):
     assert_close(ra[66:67], read(1), FP32_TOL, "step 1")
     assert_close(np.stack([ra[67], rb[8]]), read(2), FP32_TOL, "step 2")
     assert_close(ra[68:69], read(3), FP32_TOL, "step 3")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_looped_latent_layer_decodes_with_a_cache_a_pass(models, dtype):
+    """One latent layer run twice: each pass keeps latent rows of its own, and decoding reads both."""
+    _, cfg, W = models["latent"]
+    eng = engine(models, "latent", dtype)
+    assert len(eng.cache.plan.groups) == 1 and len(eng.cache.plan.groups[0].entries) == 2
+    toks = tokens_for(cfg, 150, 5)
+    close(plain.forward(cfg, W, toks), run_pieces(eng, toks, [3, 70] + list(range(100, 150))), dtype, f"looped latent {dtype}",
+          whole=run_pieces(eng, toks, []))
