@@ -128,7 +128,15 @@ struct HeadLinearArgs {
     int T, H, n_in, n_out;
     int ld_in, head_in, in_off;      // input: row stride, distance between heads, first column inside a head
     int ld_out, head_out, out_off;   // output likewise
+    const void* gate;                // null, or rows in the activation type: head h's output is multiplied by
+    int ld_gate;                     // sigmoid(gate[t * ld_gate + h]) on the accumulator, before it is rounded
 };
+
+template <typename T>
+__device__ __forceinline__ float head_gate_of(const HeadLinearArgs& a, int t, int h) {
+    if (a.gate == nullptr) return 1.0f;
+    return 1.0f / (1.0f + expf(-to_f32(static_cast<const T*>(a.gate)[(size_t)t * a.ld_gate + h])));
+}
 
 // grid (token tiles, heads, output tiles); W is [H][n_out][n_in]
 template <typename T>
@@ -148,10 +156,11 @@ head_linear_kernel(const T* __restrict__ in, const T* __restrict__ W, T* __restr
         const int t = t0 + ty + 16 * i;
         if (t >= a.T) continue;
         T* o = out + (size_t)t * a.ld_out + (size_t)h * a.head_out + a.out_off;
+        const float gt = head_gate_of<T>(a, t, h);
 #pragma unroll
         for (int j = 0; j < BN / 16; j++) {
             const int c = c0 + tx + 16 * j;
-            if (c < a.n_out) o[c] = from_f32<T>(acc[i][j]);
+            if (c < a.n_out) o[c] = from_f32<T>(a.gate != nullptr ? acc[i][j] * gt : acc[i][j]);
         }
     }
 }
@@ -189,12 +198,13 @@ head_linear_mma_kernel(const bf16* __restrict__ in, const bf16* __restrict__ W, 
             const int r = row_s[m * 16 + g + 8 * half];
             if (r < 0) continue;
             bf16* o = out + (size_t)r * a.ld_out + (size_t)h * a.head_out + a.out_off;
+            const float gt = head_gate_of<bf16>(a, r, h);
 #pragma unroll
             for (int j = 0; j < NT; j++)
 #pragma unroll
                 for (int q = 0; q < 2; q++) {
                     const int c = c0 + j * 8 + 2 * t + q;
-                    if (c < a.n_out) o[c] = from_f32<bf16>(acc[0][m][j][2 * half + q]);
+                    if (c < a.n_out) o[c] = from_f32<bf16>(a.gate != nullptr ? acc[0][m][j][2 * half + q] * gt : acc[0][m][j][2 * half + q]);
                 }
         }
 }
@@ -245,13 +255,25 @@ MYNAH_API int mynah_latent_prep(const void* q, int ldq, int q_off, const void* d
     return mynah_check_launch("latent_prep");
 }
 
+MYNAH_API int mynah_head_linear_gated(const void* in, const void* W, void* out, int dtype, int T, int H, int n_in, int n_out,
+                                      int ld_in, int head_in, int in_off, int ld_out, int head_out, int out_off,
+                                      const void* gate, int ld_gate, cudaStream_t stream);
+
 MYNAH_API int mynah_head_linear(const void* in, const void* W, void* out, int dtype, int T, int H, int n_in, int n_out,
                                 int ld_in, int head_in, int in_off, int ld_out, int head_out, int out_off,
                                 cudaStream_t stream) {
+    return mynah_head_linear_gated(in, W, out, dtype, T, H, n_in, n_out, ld_in, head_in, in_off, ld_out, head_out, out_off,
+                                   nullptr, 0, stream);
+}
+
+// The same with every head's output multiplied by sigmoid(gate[t][h]) (gate: rows in the activation type, or null).
+MYNAH_API int mynah_head_linear_gated(const void* in, const void* W, void* out, int dtype, int T, int H, int n_in, int n_out,
+                                      int ld_in, int head_in, int in_off, int ld_out, int head_out, int out_off,
+                                      const void* gate, int ld_gate, cudaStream_t stream) {
     if (T == 0) return 0;
     MYNAH_REQUIRE(T > 0 && H > 0 && n_in > 0 && n_out > 0, "head_linear: bad sizes");
     MYNAH_REQUIRE(H <= 65535 && ceil_div(n_out, 64) <= 65535, "head_linear: too many heads or outputs for one launch");
-    const HeadLinearArgs a{T, H, n_in, n_out, ld_in, head_in, in_off, ld_out, head_out, out_off};
+    const HeadLinearArgs a{T, H, n_in, n_out, ld_in, head_in, in_off, ld_out, head_out, out_off, gate, ld_gate};
     const bool mma_ok = dtype == MYNAH_BF16 && !g_head_linear_plain && n_in % 8 == 0 && ld_in % 8 == 0 && head_in % 8 == 0 &&
                         in_off % 8 == 0 && (((uintptr_t)in | (uintptr_t)W) & 15) == 0 && ceil_div(n_out, 128) <= 65535;
     if (mma_ok) {

@@ -877,9 +877,11 @@ def latent_prep(q: torch.Tensor, q_off: int, dkv: Optional[torch.Tensor], dkv_of
 
 
 def head_linear(x: torch.Tensor, head_in: int, in_off: int, W: torch.Tensor, out: torch.Tensor, head_out: int,
-                out_off: int) -> torch.Tensor:
+                out_off: int, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t, h * head_out + out_off + j] = sum_i W[h, j, i] * x[t, h * head_in + in_off + i]: one small product a head
-    (csrc/latent_attn.cu). W [H, n_out, n_in] in the rows' type; fp32 accumulation."""
+    (csrc/latent_attn.cu). W [H, n_out, n_in] in the rows' type; fp32 accumulation. With `gate` (rows of H logits in
+    the rows' type; a column slice is fine) head h's outputs are multiplied by sigmoid(gate[t, h]) before they are
+    rounded."""
     _rows(x, "head_linear: input")
     _rows(out, "head_linear: output")
     _chk(W, "head_linear: weights", x.dtype, 3)
@@ -888,8 +890,13 @@ def head_linear(x: torch.Tensor, head_in: int, in_off: int, W: torch.Tensor, out
     H, n_out, n_in = W.shape
     if (H - 1) * head_in + in_off + n_in > x.shape[1] or (H - 1) * head_out + out_off + n_out > out.shape[1]:
         raise KernelError("head_linear: the heads do not fit the rows")
-    call("mynah_head_linear", ptr(x), ptr(W), ptr(out), code(x.dtype), x.shape[0], H, n_in, n_out,
-         x.stride(0), head_in, in_off, out.stride(0), head_out, out_off, stream_ptr())
+    if gate is not None:
+        _rows(gate, "head_linear: gate")
+        if gate.dtype != x.dtype or gate.shape[0] != x.shape[0] or gate.shape[1] < H:
+            raise KernelError("head_linear: the gate's rows do not fit the heads")
+    call("mynah_head_linear_gated", ptr(x), ptr(W), ptr(out), code(x.dtype), x.shape[0], H, n_in, n_out,
+         x.stride(0), head_in, in_off, out.stride(0), head_out, out_off, ptr(gate), gate.stride(0) if gate is not None else 0,
+         stream_ptr())
     return out
 
 

@@ -125,6 +125,7 @@ _SIGNATURES: dict[str, list] = {
     "mynah_latent_prep": [P, c_int, c_int, P, c_int, c_int, c_int, P, c_int, c_int, c_int, c_int, c_int, c_int,
                           P, c_int, c_float, P, P, c_int, c_int, c_int, P, P, P, P, P, c_int, P, P, P],
     "mynah_head_linear": [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P],
+    "mynah_head_linear_gated": [P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, P, c_int, P],
     "mynah_retention_prep": [P, c_int, c_int, c_int, c_int, P, P, c_int, c_int, c_int, P, P, c_int, c_int, c_int,
                              c_float, P, P, P, P],
     "mynah_retention_scan": [P, P, P, c_int, c_int, c_int, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, P, P],

@@ -141,9 +141,9 @@ class LatentAttention(Mixer):
             attention_dispatch.prefill_masked(q, lat, ctx, H, 1, HDp, HDp, cache.k, cache.k, pages, self.window or 0, 0,
                                               self.scale)
         v = torch.empty((T, H * self.vd), dtype=p.dtype, device=p.device)
-        kernels.head_linear(lat, HDp, 0, self.w_uv, v, self.vd, 0)
-        if self.gate_name:
-            kernels.head_gate(v, p[:, self.gate_off: self.gate_off + H], H, self.vd)
+        # the gate rides on the value product's accumulators
+        kernels.head_linear(lat, HDp, 0, self.w_uv, v, self.vd, 0,
+                            gate=p[:, self.gate_off: self.gate_off + H] if self.gate_name else None)
         return kernels.linear(v, self.w_o)
 
 

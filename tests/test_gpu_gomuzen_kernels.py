@@ -244,6 +244,21 @@ def test_head_gate(dtype, H, vd, off):
     assert rel(ref, x.double().cpu().numpy()) < (1e-6 if dtype == torch.float32 else 1e-2)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("T,H,n_in,n_out", [(70, 3, 16, 40), (1, 1, 6, 13), (200, 16, 96, 128), (9, 2, 64, 24)])
+def test_head_linear_with_the_gate_on_its_accumulators(dtype, T, H, n_in, n_out):
+    from mynah_slm_b200.ops import kernels
+    rng = np.random.default_rng(T + n_in)
+    x = torch.tensor(rng.normal(size=(T, H * n_in)), dtype=dtype, device=DEV)
+    W = torch.tensor(rng.normal(size=(H, n_out, n_in)) / np.sqrt(n_in), dtype=dtype, device=DEV)
+    p = torch.tensor(2.0 * rng.normal(size=(T, 8 + H + 3)), dtype=dtype, device=DEV)
+    out = torch.zeros((T, H * n_out), dtype=dtype, device=DEV)
+    kernels.head_linear(x, n_in, 0, W, out, n_out, 0, gate=p[:, 8:8 + H])
+    ref = np.einsum("thi,hji->thj", x.double().cpu().numpy().reshape(T, H, n_in), W.double().cpu().numpy())
+    ref = ref * plain.sigmoid(p.double().cpu().numpy()[:, 8:8 + H])[..., None]
+    assert rel(ref.reshape(T, -1), out.double().cpu().numpy()) < (1e-5 if dtype == torch.float32 else 1e-2)
+
+
 def test_residual_add_row():
     from mynah_slm_b200.ops import kernels
     rng = np.random.default_rng(3)
