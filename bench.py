@@ -372,7 +372,7 @@ def gomuzen_config(shape: str, layers: int) -> dict:
     c.update(SHAPES[shape])
     D, H, G, HD, F = c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"], c["intermediate_size"]
     moe = {"kind": "moe", "expert": {"ff": F // 2, "limit": 7.0},
-           "router": {"experts": 16, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+           "router": {"experts": 16, "top": 2, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
     yarn = {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}
     lat = {"type": "latent_attention", "mlp": moe, "mixer": {
         "heads": H, "dim": HD - 32, "rot_dim": 32, "vdim": HD, "kv_rank": 96, "scale": HD ** -0.5,

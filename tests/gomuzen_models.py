@@ -72,24 +72,24 @@ ODD = config(44, 131, [
 ], eps=1e-3, loop=(0, 2, 1))
 # no loop at all
 PLAIN = config(48, 200, [
-    moe(windowed(4, 2, 8, 8, 0.3, 20.0, 8, window=33, keep_first=3), 24, 1.5, 4, 2, 2.5, groups=(2, 1)),
+    moe(windowed(4, 2, 8, 8, 0.3, 20.0, 8, window=33, keep_first=3), 24, 1.3, 4, 2, 2.2, groups=(2, 1)),
     bare(latent(2, 8, 8, 8, 16, 0.25, base=300.0)),
 ])
 ONLY_LATENT = config(48, 200, [bare(latent(4, 16, 8, 8, 24, 0.25, base=300.0, scaling=(8.0, 32, 8.0, 2.0)))], loop=(0, 1, 2))      # the one layer twice
 ONLY_DIFF = config(48, 200, [bare(differential(4, 2, 16, 12, 0.25, 12.0, 0.4, 12, base=1000.0))])
 ONLY_WINDOW = config(48, 200, [bare(windowed(4, 2, 16, 12, 0.25, 12.0, 16, base=1000.0, scaling=(8.0, 32, 8.0, 2.0), window=50, keep_first=7))])
 ONLY_SLIDE = config(48, 200, [bare(windowed(4, 2, 16, 12, 0.25, 12.0, 16, base=1000.0, window=70))])      # nothing kept: pages go back
-ONLY_MOE = config(48, 200, [moe(windowed(1, 1, 8, 8, 0.3, 5.0, 8), 56, 1.2, 12, 3, 2.5, groups=(4, 2))])
+ONLY_MOE = config(48, 200, [moe(windowed(1, 1, 8, 8, 0.3, 5.0, 8), 56, 1.2, 12, 3, 1.9, groups=(4, 2))])
 # attention whose softmax is sharp (large query and key weights, a cap far above the scores): one key stands out
 SHARP = config(64, 150, [
-    bare(windowed(4, 2, 16, 16, 1.0, 200.0, 16, base=1000.0, window=72, keep_first=10)),
+    bare(windowed(4, 2, 16, 16, 1.0, 200.0, 16, base=1000.0, window=76, keep_first=10)),
     bare(differential(2, 1, 16, 16, 1.0, 200.0, 0.3, 16, base=1000.0)),
     bare(latent(4, 16, 16, 16, 32, 1.0, base=1000.0)),
     bare(windowed(2, 2, 16, 8, 1.0, 200.0, 8, base=1000.0, window=130, keep_first=66)),
 ])
 # heads of 64 and 128 with equal keys and values, cache rows of 128: the sizes the tensor-core attention kernels take
 WIDE = config(128, 200, [
-    moe(windowed(4, 2, 64, 64, 0.125, 20.0, 64, window=100, keep_first=12), 64, 2.0, 8, 2, 2.0, groups=(2, 1)),
+    moe(windowed(4, 2, 64, 64, 0.125, 18.0, 64, window=100, keep_first=12), 64, 2.0, 8, 2, 2.0, groups=(4, 2)),
     bare(differential(2, 1, 64, 64, 0.125, 30.0, 0.5, 32)),
     bare(latent(16, 16, 32, 8, 96, 0.2, base=500.0, scaling=(2.0, 128, 32.0, 1.0))),
     bare(windowed(2, 1, 128, 128, 0.09, 50.0, 128, window=200, keep_first=70)),
